@@ -372,3 +372,92 @@ def read_config_json(model_dir) -> dict:
         return json.loads(path.read_text())
     except json.JSONDecodeError as e:
         raise ConfigError(f"{path} is not valid JSON: {e}") from e
+
+
+@dataclass(frozen=True)
+class NonetarLayerConfig:
+    """One entry of ``layers``: the mixer's kind (``parallel`` or ``mamba2``) and sizes, and the
+    feed-forward (None: the layer has only its mixer)."""
+    type: str
+    mixer: Mapping[str, Any]
+    mlp: Optional[Mapping[str, Any]]
+
+
+_NONETAR_MIXER_KEYS = {
+    "parallel": ("left", "right", "left_scale", "right_scale"),
+    "mamba2": ("heads", "vdim", "state", "groups", "norm_groups", "conv"),
+}
+_NONETAR_LEFT_KEYS = ("heads", "kv_heads", "dim", "vdim", "scale")
+_NONETAR_RIGHT_KEYS = ("width", "blocks", "conv")
+
+
+@dataclass(frozen=True)
+class NonetarConfig:
+    """The keys of a Nonetar config.json: ``vocab``, ``width``, ``norm.eps``, ``streams`` (copies of the
+    residual stream), ``logit_scale`` and ``layers`` (each with ``type``, ``mixer`` and ``mlp``, the
+    latter of ``kind`` ``dense`` or null).  A ``parallel`` mixer names a ``left`` side (attention:
+    ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, and optionally ``softcap`` and ``mask.size``), a
+    ``right`` side (gated linear recurrence: ``width``, ``blocks``, ``conv``) and their weights in the sum;
+    a ``mamba2`` mixer names ``heads``, ``vdim``, ``state``, ``groups``, ``norm_groups`` and ``conv``."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    streams: int
+    logit_scale: float
+    layers: Tuple[NonetarLayerConfig, ...]
+    max_position_embeddings: int
+    eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "NonetarConfig":
+        norm = d.get("norm") or {}
+        layers = []
+        for i, entry in enumerate(d.get("layers") or []):
+            kind = entry.get("type")
+            if kind not in _NONETAR_MIXER_KEYS:
+                raise ConfigError(f"config.json: layer {i} has a mixer of type {kind!r}; known: "
+                                  + ", ".join(sorted(_NONETAR_MIXER_KEYS)))
+            mixer = entry.get("mixer") or {}
+            for key in _NONETAR_MIXER_KEYS[kind]:
+                if mixer.get(key) is None:
+                    raise ConfigError(f"config.json: layer {i} ({kind}): mixer key {key!r} is missing")
+            if kind == "parallel":
+                for side, keys in (("left", _NONETAR_LEFT_KEYS), ("right", _NONETAR_RIGHT_KEYS)):
+                    for key in keys:
+                        if mixer[side].get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mixer.{side}.{key} is missing")
+                left, right = mixer["left"], mixer["right"]
+                if int(left["heads"]) % int(left["kv_heads"]):
+                    raise ConfigError(f"config.json: layer {i}: {left['heads']} query heads cannot be grouped over "
+                                      f"{left['kv_heads']} key/value heads")
+                if int(right["width"]) % int(right["blocks"]):
+                    raise ConfigError(f"config.json: layer {i}: {right['width']} channels do not split into "
+                                      f"{right['blocks']} equal blocks")
+            else:
+                if int(mixer["heads"]) % int(mixer["groups"]):
+                    raise ConfigError(f"config.json: layer {i}: {mixer['heads']} heads cannot share "
+                                      f"{mixer['groups']} groups evenly")
+                if (int(mixer["heads"]) * int(mixer["vdim"])) % int(mixer["norm_groups"]):
+                    raise ConfigError(f"config.json: layer {i}: the inner width does not split into "
+                                      f"{mixer['norm_groups']} equal parts")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ConfigError(f"config.json: layer {i}: a feed-forward of kind {mlp.get('kind')!r} is not known "
+                                      "(known: 'dense')")
+                _need(mlp, "ff", int)
+            layers.append(NonetarLayerConfig(str(kind), dict(mixer), dict(mlp) if mlp is not None else None))
+        if not layers:
+            raise ConfigError("config.json: 'layers' is missing or empty")
+        eos = d.get("eos_token_id")
+        eos_ids = () if eos is None else (tuple(int(e) for e in eos) if isinstance(eos, (list, tuple)) else (int(eos),))
+        cfg = cls(architecture=str(d.get("architecture") or (d.get("architectures") or ["Nonetar"])[0]),
+                  vocab=_need(d, "vocab", int), width=_need(d, "width", int), norm_eps=_need(norm, "eps", float),
+                  streams=int(d["streams"]) if d.get("streams") is not None else 1,
+                  logit_scale=float(d["logit_scale"]) if d.get("logit_scale") is not None else 1.0,
+                  layers=tuple(layers), max_position_embeddings=int(d.get("max_position_embeddings") or 131072),
+                  eos_token_ids=eos_ids)
+        if cfg.vocab < 1 or cfg.width < 1 or not cfg.norm_eps > 0 or cfg.streams < 1:
+            raise ConfigError("config.json: vocab, width and streams must be positive and norm.eps above zero")
+        return cfg

@@ -375,7 +375,8 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* 
                                  const float* __restrict__ tails, long long slot_stride, T* __restrict__ out, int C,
                                  const int* __restrict__ positions, const int* __restrict__ token_req,
                                  const int* __restrict__ q_start, const int* __restrict__ req_start,
-                                 const int* __restrict__ slots, int act) {
+                                 const int* __restrict__ slots, int act, const float* __restrict__ in_bias,
+                                 const float* __restrict__ out_bias) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -384,9 +385,13 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* 
   const int pos = positions[t], r = token_req[t];
   const int start = req_start[r], row0 = q_start[r];
   const float* tail = tails + (size_t)slots[r] * slot_stride;
-  float acc = 0.f;
-  for (int j = 0; j < taps; ++j)
-    acc = fmaf(w[(size_t)c * taps + j], conv_input(in, ld, tail, C, c, pos - (taps - 1) + j, start, row0, taps), acc);
+  const float ib = in_bias ? in_bias[c] : 0.f;      // joins every input that exists (not the zeros before the start)
+  float acc = out_bias ? out_bias[c] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int sp = pos - (taps - 1) + j;
+    if (sp < 0) continue;
+    acc = fmaf(w[(size_t)c * taps + j], conv_input(in, ld, tail, C, c, sp, start, row0, taps) + ib, acc);
+  }
   out[(size_t)t * C + c] = from_f32<T>(act == 0 ? acc / (1.0f + expf(-acc)) : acc);
 }
 
@@ -434,7 +439,8 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
                                 const float* __restrict__ tails, long long slot_stride, T* __restrict__ out, int C,
                                 int T_, const int* __restrict__ positions, const int* __restrict__ token_req,
                                 const int* __restrict__ q_start, const int* __restrict__ req_start,
-                                const int* __restrict__ slots, int act, AppendArgs ap) {
+                                const int* __restrict__ slots, int act, AppendArgs ap,
+                                const float* __restrict__ in_bias, const float* __restrict__ out_bias) {
   constexpr int VEC = Vec16<T>::N;
   pdl_trigger();
   pdl_wait();
@@ -458,9 +464,12 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
 #pragma unroll
     for (int e = 0; e < VEC; ++e) x[e] = tp[e];
   };
-  float acc[VEC];
+  float acc[VEC], ib[VEC];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+  for (int e = 0; e < VEC; ++e) {
+    acc[e] = out_bias ? out_bias[c + e] : 0.f;
+    ib[e] = in_bias ? in_bias[c + e] : 0.f;         // joins every input that exists (not the zeros before the start)
+  }
   if (TAPS > 0) {
     constexpr int NT = TAPS > 0 ? TAPS : 1;
     float wv[VEC * NT];                       // channel e's taps at wv[e * NT ..]; c * NT floats is a multiple of 16 bytes
@@ -481,6 +490,10 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
       float x[VEC];
       if (same[j]) Vec16<T>::load(in + (size_t)(t - back) * ld + c, x);
       else older(back, x);
+      if (pos - back >= 0) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] += ib[e];
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wv[e * NT + j], x[e], acc[e]);
     }
@@ -490,6 +503,10 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
       float x[VEC];
       if (back == 0 || (t - back >= 0 && token_req[t - back] == r)) Vec16<T>::load(in + (size_t)(t - back) * ld + c, x);
       else older(back, x);
+      if (pos - back >= 0) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] += ib[e];
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], x[e], acc[e]);
     }
@@ -546,11 +563,14 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, int ld, int taps, flo
 // of whole 16-byte groups can: the launcher refuses otherwise and the caller writes them with a kernel of its own).
 // in: [T, >= C] with row stride ld; w [C, taps] float32; tails: the tail of slot 0, slot_stride
 // floats from slot to slot, each [taps - 1, C]; out [T, C] dense.  act: 0 SiLU behind the sum, 1 the
-// bare sum.  Refuses taps > 16.
+// bare sum.  in_bias (float32 [C] or null) joins every input before it is weighed (the inputs before a
+// sequence's start stay zero; the tails keep the inputs without it), out_bias (float32 [C] or null) joins
+// the sum.  Refuses taps > 16.
 KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, float* tails, long long slot_stride,
                              void* out, int C, int T_, int R, const int* positions, const int* token_req,
                              const int* q_start, const int* req_start, const int* ctx_len, const int* slots,
-                             int act, const AppendArgs* append, int dtype, cudaStream_t stream) {
+                             int act, const AppendArgs* append, const float* in_bias, const float* out_bias, int dtype,
+                             cudaStream_t stream) {
   if (T_ <= 0 || R <= 0) return 0;
   if (taps < 1 || taps - 1 > kMaxTail || C < 1 || act < 0 || act > 1) return KVB_ERR_BAD_SIZE;
   const int threads = 128;
@@ -570,7 +590,8 @@ KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, f
     const bool w16 = ((uintptr_t)w % 16) == 0;
 #define KVB_CONV(TAPS)                                                                                                  \
   kvb_launch(conv_vec_kernel<T, TAPS>, dim3((unsigned)((units + 255) / 256)), dim3(256), 0, stream, (const T*)in, ld, w, \
-             taps, (const float*)tails, slot_stride, (T*)out, C, T_, positions, token_req, q_start, req_start, slots, act, ap)
+             taps, (const float*)tails, slot_stride, (T*)out, C, T_, positions, token_req, q_start, req_start, slots, act, ap, \
+             in_bias, out_bias)
     KVB_DISPATCH_DTYPE(dtype, T, {
       if (taps == 2 && w16) KVB_CONV(2);
       else if (taps == 3 && w16) KVB_CONV(3);
@@ -585,7 +606,8 @@ KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, f
   }
   KVB_DISPATCH_DTYPE(dtype, T, {
     kvb_launch(conv_silu_kernel<T>, dim3(T_, by), dim3(threads), 0, stream, (const T*)in, ld, w, taps,
-               (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots, act);
+               (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots, act, in_bias,
+               out_bias);
     if (taps > 1)
       kvb_launch(conv_tail_kernel<T>, dim3(R, by), dim3(threads), 0, stream, (const T*)in, ld, taps, tails, slot_stride,
                  C, q_start, req_start, ctx_len, slots);

@@ -20,6 +20,24 @@
 constexpr int kMaxDim = 256;
 constexpr int kWarps = 4;
 
+// What a mixer may do to a score between the scaled dot product and the softmax, in this order: a factor
+// per query head, a soft cap (cap * tanh(s / cap)), and a bias that grows with the distance between query
+// and key (s - slope_h * (i - j)).  Null pointers and a cap of 0 leave the score as it is.  out_scale
+// multiplies the attention's result (the weight of this mixer where two run side by side).
+struct ScoreShape {
+  const float* head_scale;   // [heads] or null
+  const float* slopes;       // [heads] or null
+  float softcap;             // 0: none
+  float out_scale;           // 1: none
+};
+
+__device__ __forceinline__ float shape_score(float s, const ScoreShape& sh, int head, int dist) {
+  if (sh.head_scale != nullptr) s *= sh.head_scale[head];
+  if (sh.softcap > 0.f) s = sh.softcap * tanhf(s / sh.softcap);
+  if (sh.slopes != nullptr) s = fmaf(-sh.slopes[head], (float)dist, s);
+  return s;
+}
+
 // Writes the step's keys and values into their requests' pages.  src [T, >= ...] holds, per token, the
 // keys of all kv heads from column k_off on (G * Dk) and the values from v_off on (G * Dv).
 template <typename T>
@@ -101,7 +119,7 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
                         const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
                         const int* __restrict__ positions, const int* __restrict__ token_req, T* __restrict__ out,
                         int nq, int nkv, int Dk, int Dv, float scale, int window, int keep_first, int one_more,
-                        int vec, int* status) {
+                        int vec, ScoreShape shape, int* status) {
   __shared__ float q_s[kMaxDim];
   __shared__ float acc_s[kWarps][kMaxDim];
   __shared__ float m_s[kWarps], l_s[kWarps];
@@ -145,7 +163,7 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
         atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
       } else {
         off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * row_len;
-        s = key_dot<T>(q_s, pages + off, Dk, vec != 0) * scale;
+        s = shape_score(key_dot<T>(q_s, pages + off, Dk, vec != 0) * scale, shape, h, pos - j);
       }
     }
     const float cm = warp_max(s);
@@ -190,7 +208,7 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
     for (int i = lane; i < Dv; i += 32) {
       float a = 0.f;
       for (int w = 0; w < kWarps; ++w) a += acc_s[w][i] * f[w];
-      o[i] = from_f32<T>(L > 0.f ? a / L : 0.f);
+      o[i] = from_f32<T>(L > 0.f ? a / L * shape.out_scale : 0.f);
     }
   }
 }
@@ -244,7 +262,7 @@ window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, co
                               const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
                               const int* __restrict__ positions, const int* __restrict__ token_req, T* __restrict__ out,
                               int nq, int nkv, int Dk, float scale, int window, int keep_first, int one_more, int vec,
-                              int* status) {
+                              ScoreShape shape, int* status) {
   constexpr int Dv = VPL * 32;
   extern __shared__ float gsm[];
   float* q_s = gsm;                                  // [GP][Dk]
@@ -323,7 +341,7 @@ window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, co
           }
         }
 #pragma unroll
-        for (int g = 0; g < GP; ++g) s[g] = dot[g] * scale;
+        for (int g = 0; g < GP; ++g) s[g] = g < G ? shape_score(dot[g] * scale, shape, hk * G + g, pos - j) : 0.f;
       }
     }
     if (warp_max(off >= 0 ? 1.f : -CUDART_INF_F) == -CUDART_INF_F) continue;   // nothing readable in this chunk
@@ -385,7 +403,7 @@ window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, co
     for (int i = lane; i < Dv; i += 32) {
       float a = 0.f;
       for (int w = 0; w < kGroupWarps; ++w) a += acc_s[(w * GP + g) * Dv + i] * f[w];
-      o[i] = from_f32<T>(L > 0.f ? a / L : 0.f);
+      o[i] = from_f32<T>(L > 0.f ? a / L * shape.out_scale : 0.f);
     }
   }
 }
@@ -394,7 +412,7 @@ template <typename T, int VPL, int GP>
 static int launch_group(const void* q, int q_row_stride, const void* pages, const int* block_table, int max_pages,
                         int page_size, int num_pages, const int* positions, const int* token_req, void* out, int T_,
                         int nq, int nkv, int Dk, float scale, int window, int keep_first, int one_more, int vec,
-                        int* status, cudaStream_t stream) {
+                        ScoreShape shape, int* status, cudaStream_t stream) {
   const size_t smem = ((size_t)GP * Dk + (size_t)kGroupWarps * GP * (VPL * 32 + 2)) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(window_attention_group_kernel<T, VPL, GP>,
@@ -403,7 +421,7 @@ static int launch_group(const void* q, int q_row_stride, const void* pages, cons
   }
   kvb_launch(window_attention_group_kernel<T, VPL, GP>, dim3(T_, nkv), dim3(kGroupWarps * 32), smem, stream, (const T*)q,
              q_row_stride, (const T*)pages, block_table, max_pages, page_size, num_pages, positions, token_req, (T*)out, nq,
-             nkv, Dk, scale, window, keep_first, one_more, vec, status);
+             nkv, Dk, scale, window, keep_first, one_more, vec, shape, status);
   return kvb_launch_result();
 }
 
@@ -411,10 +429,10 @@ template <typename T, int VPL>
 static int launch_group_gp(int G, const void* q, int q_row_stride, const void* pages, const int* block_table,
                            int max_pages, int page_size, int num_pages, const int* positions, const int* token_req,
                            void* out, int T_, int nq, int nkv, int Dk, float scale, int window, int keep_first,
-                           int one_more, int vec, int* status, cudaStream_t stream) {
+                           int one_more, int vec, ScoreShape shape, int* status, cudaStream_t stream) {
 #define KVB_WG(GP) return launch_group<T, VPL, GP>(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, \
                                                    positions, token_req, out, T_, nq, nkv, Dk, scale, window, keep_first, \
-                                                   one_more, vec, status, stream)
+                                                   one_more, vec, shape, status, stream)
   if (G == 1) KVB_WG(1);
   if (G == 2) KVB_WG(2);
   if (G <= 4) KVB_WG(4);
@@ -425,11 +443,11 @@ static int launch_group_gp(int G, const void* q, int q_row_stride, const void* p
 // q points at the first query head of token 0; consecutive tokens are q_row_stride elements apart.
 // pages: [num_pages, nkv, page_size, Dk + Dv].  out is [T, nq * Dv], dense.
 // Refuses: Dk or Dv above 256, nq not a multiple of nkv, a negative window or keep_first.
-KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void* pages, const int* block_table,
-                                    int max_pages, int page_size, int num_pages, const int* positions,
-                                    const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
-                                    float scale, int window, int keep_first, int one_more, int dtype, int* status,
-                                    cudaStream_t stream) {
+static int window_attention_any(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                int max_pages, int page_size, int num_pages, const int* positions,
+                                const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
+                                float scale, int window, int keep_first, int one_more, ScoreShape shape, int dtype,
+                                int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (Dk > kMaxDim || Dv > kMaxDim || Dk < 1 || Dv < 1 || nkv < 1 || nq % nkv || window < 0 || keep_first < 0)
     return KVB_ERR_BAD_SIZE;
@@ -443,7 +461,7 @@ KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void*
   KVB_DISPATCH_DTYPE(dtype, T, return (launch_group_gp<T, VPL>(G, q, q_row_stride, pages, block_table, max_pages,      \
                                                                page_size, num_pages, positions, token_req, out, T_, nq, \
                                                                nkv, Dk, scale, window, keep_first, one_more, vec,      \
-                                                               status, stream)))
+                                                               shape, status, stream)))
     if (Dv == 32) { KVB_WV(1); }
     if (Dv == 64) { KVB_WV(2); }
     if (Dv == 128) { KVB_WV(4); }
@@ -453,6 +471,110 @@ KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void*
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(window_attention_kernel<T>, grid, dim3(kWarps * 32), 0, stream, (const T*)q,
                                             q_row_stride, (const T*)pages, block_table, max_pages, page_size, num_pages,
                                             positions, token_req, (T*)out, nq, nkv, Dk, Dv, scale, window, keep_first,
-                                            one_more, vec, status)));
+                                            one_more, vec, shape, status)));
+  return kvb_launch_result();
+}
+
+KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                    int max_pages, int page_size, int num_pages, const int* positions,
+                                    const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
+                                    float scale, int window, int keep_first, int one_more, int dtype, int* status,
+                                    cudaStream_t stream) {
+  const ScoreShape plain = {nullptr, nullptr, 0.f, 1.f};
+  return window_attention_any(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, positions, token_req,
+                              out, T_, nq, nkv, Dk, Dv, scale, window, keep_first, one_more, plain, dtype, status, stream);
+}
+
+// The same with the scores shaped on their way to the softmax (see ScoreShape): head_scale and slopes are
+// float32 [nq] or null, softcap 0 for none, out_scale multiplies the result.
+KVB_EXPORT int kvb_window_attention_shaped(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                           int max_pages, int page_size, int num_pages, const int* positions,
+                                           const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
+                                           float scale, int window, int keep_first, int one_more,
+                                           const float* head_scale, const float* slopes, float softcap, float out_scale,
+                                           int dtype, int* status, cudaStream_t stream) {
+  if (softcap < 0.f) return KVB_ERR_BAD_SIZE;
+  const ScoreShape shape = {head_scale, slopes, softcap, out_scale};
+  return window_attention_any(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, positions, token_req,
+                              out, T_, nq, nkv, Dk, Dv, scale, window, keep_first, one_more, shape, dtype, status, stream);
+}
+
+// ---------------------------------------------------------------- biases, per-head norms and the cache write
+// src [T, ld] holds, per token, nq queries of Dk from column 0, nkv keys of Dk from k_off and nkv values of Dv from
+// v_off, as a product left them.  Each gets its bias (float32, may be null); every query and key head is then
+// divided by its root mean square (eps inside the root) and multiplied by a weight of Dk shared by the heads
+// (qw, kw; null: no norm).  Queries go to q_out [T, nq * Dk]; keys and values into the request's pages, a row
+// [key | value] per token and key/value head.  One block per token, a warp per head.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_append_kernel(const T* __restrict__ src, int ld, int k_off, int v_off, const float* __restrict__ bq,
+                      const float* __restrict__ bk, const float* __restrict__ bv, const float* __restrict__ qw,
+                      const float* __restrict__ kw, float eps, T* __restrict__ q_out, T* __restrict__ pages,
+                      const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                      const int* __restrict__ positions, const int* __restrict__ token_req, int nq, int nkv, int Dk,
+                      int Dv, int write, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T* row = src + (size_t)t * ld;
+  const int pos = positions[t];
+  const int lp = pos / page_size;
+  int page = -1;
+  if (write) {
+    page = lp < max_pages ? block_table[(size_t)token_req[t] * max_pages + lp] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      page = -1;
+    }
+  }
+  for (int unit = warp; unit < nq + 2 * nkv; unit += nw) {
+    const bool is_q = unit < nq, is_k = !is_q && unit < nq + nkv;
+    const int head = is_q ? unit : (is_k ? unit - nq : unit - nq - nkv);
+    const int D = (is_q || is_k) ? Dk : Dv;
+    const T* x = row + (is_q ? head * Dk : (is_k ? k_off + head * Dk : v_off + head * Dv));
+    const float* bias = is_q ? bq : (is_k ? bk : bv);
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nq + head) * Dk;
+    } else {
+      if (page < 0) continue;
+      dst = pages + (((size_t)page * nkv + head) * page_size + (pos % page_size)) * (Dk + Dv) + (is_k ? 0 : Dk);
+    }
+    float v[kMaxDim / 32];
+    float sq = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxDim / 32; ++r) {
+      const int i = r * 32 + lane;
+      v[r] = 0.f;
+      if (i < D) {
+        v[r] = to_f32(x[i]) + (bias ? bias[head * D + i] : 0.f);
+        sq = fmaf(v[r], v[r], sq);
+      }
+    }
+    float f = 1.f;
+    if (w != nullptr) f = 1.0f / sqrtf(warp_sum(sq) / (float)D + eps);
+#pragma unroll
+    for (int r = 0; r < kMaxDim / 32; ++r) {
+      const int i = r * 32 + lane;
+      if (i < D) dst[i] = from_f32<T>(w != nullptr ? v[r] * f * w[i] : v[r]);
+    }
+  }
+}
+
+KVB_EXPORT int kvb_qk_norm_append(const void* src, int ld, int k_off, int v_off, const float* bq, const float* bk,
+                                  const float* bv, const float* qw, const float* kw, float eps, void* q_out, void* pages,
+                                  const int* block_table, int max_pages, int page_size, int num_pages,
+                                  const int* positions, const int* token_req, int T_, int nq, int nkv, int Dk, int Dv,
+                                  int write, int dtype, int* status, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (Dk > kMaxDim || Dv > kMaxDim || Dk < 1 || Dv < 1 || nkv < 1 || nq < 1) return KVB_ERR_BAD_SIZE;
+  const int units = nq + 2 * nkv;
+  const int threads = units >= 8 ? 256 : 32 * units;
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(qk_norm_append_kernel<T>, dim3(T_), dim3(threads), 0, stream, (const T*)src, ld,
+                                            k_off, v_off, bq, bk, bv, qw, kw, eps, (T*)q_out, (T*)pages, block_table,
+                                            max_pages, page_size, num_pages, positions, token_req, nq, nkv, Dk, Dv, write,
+                                            status)));
   return kvb_launch_result();
 }

@@ -91,11 +91,12 @@ class DecoderModel:
     def arena_bytes(self, max_tokens: int, max_logit_rows: int):
         """(bytes that live for a whole step, bytes that one layer produces) for steps of up to
         ``max_tokens`` tokens with up to ``max_logit_rows`` rows of logits: the residual in
-        float32, the picked rows and their logits; and per layer the widths its parts declare
+        float32 (every copy of it, where the model keeps several), the picked rows and their logits; and per layer the widths its parts declare
         (``activation_widths``; a part that declares none is taken as eight rows of the model's
         width) in the compute precision, plus a fifth."""
         h, v = self.spec.hidden_size, self.spec.vocab_size
-        step = 4 * max_tokens * h * (2 if self.keeps_embedding else 1) + max_logit_rows * 4 * (h + v) + (1 << 16)
+        copies = int(getattr(self.embedding, "stream_copies", 1))      # a residual stream kept as several copies
+        step = 4 * max_tokens * h * (copies + (1 if self.keeps_embedding else 0)) + max_logit_rows * 4 * (h + v) + (1 << 16)
         per_layer = 0
         for block in self.layers:
             widths = 0

@@ -477,16 +477,21 @@ def conv_can_append(x: torch.Tensor, first: int, channels: int, k_off: int, v_of
 
 
 def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails: Optional[torch.Tensor],
-              batch, act: str = "silu", append=None) -> torch.Tensor:
+              batch, act: str = "silu", append=None, in_bias: Optional[torch.Tensor] = None,
+              out_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``silu`` (``act`` "none": nothing) of a short causal convolution over time per channel of ``x[:, first:first + channels]``.
     ``w`` float32 [channels, taps], last column for the token itself.  ``tails``: float32
     [slots, >= (taps - 1) * channels], a view whose row r starts with request slot r's last
     ``taps - 1`` inputs; it is read for the inputs in front of the step's tokens and brought up to date.
     ``append``: (pages, block_table, k_off, v_off, kv_heads, dk, dv): the results from channel ``k_off`` on are
     ``kv_heads`` keys of ``dk``, those from ``v_off`` on values of ``dv``, and they are also written into the requests'
-    pages [num_pages, kv_heads, page_size, dk + dv] (only when :func:`conv_can_append` says so)."""
+    pages [num_pages, kv_heads, page_size, dk + dv] (only when :func:`conv_can_append` says so).
+    ``in_bias`` (float32 [channels]) joins every input before it is weighed, except the zeros that stand before a
+    sequence's start; ``out_bias`` (float32 [channels]) joins the sum before the activation."""
     _need_cuda(x, w)
     taps = w.shape[1]
+    for b in (in_bias, out_bias):
+        assert b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == channels)
     assert w.dtype == torch.float32 and w.is_contiguous() and x.stride(1) == 1
     assert taps == 1 or (tails is not None and tails.dtype == torch.float32 and tails.stride(-1) == 1)
     out = new((x.shape[0], channels), x.dtype, x.device)
@@ -501,7 +506,7 @@ def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails
         c_longlong(0 if tails is None else tails.stride(0)), _p(out), c_int(channels), c_int(x.shape[0]),
         c_int(batch.num_reqs), _p(batch.positions), _p(batch.token_req), _p(batch.q_start), _p(batch.req_start),
         _p(batch.ctx_len), _p(batch.slots), c_int({"silu": 0, "none": 1}[act]),
-        ctypes.byref(ap) if ap is not None else None, c_int(dtype_code(x.dtype)), _stream())
+        ctypes.byref(ap) if ap is not None else None, _p(in_bias), _p(out_bias), c_int(dtype_code(x.dtype)), _stream())
     _check(rc, "conv_silu")
     global launch_count
     launch_count += 1 if taps > 1 else 0   # the convolution and the tails' update
@@ -674,15 +679,33 @@ def kv_rows_append(src: torch.Tensor, k_off: int, v_off: int, pages: torch.Tenso
 
 
 def window_attention(q: torch.Tensor, q_off: int, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int,
-                     dk: int, dv: int, scale: float, window: int, keep_first: int, one_more: bool) -> torch.Tensor:
+                     dk: int, dv: int, scale: float, window: int, keep_first: int, one_more: bool,
+                     head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                     softcap: float = 0.0, out_scale: float = 1.0) -> torch.Tensor:
     """Attention of every token (queries at ``q[:, q_off : q_off + heads * dk]``) over its request's cached
     rows [key | value]: query i sees key j when ``j <= i and (i - j < window or j < keep_first)`` (``window``
     0: every key up to i); ``one_more``: the softmax's denominator is ``1 + sum exp(s)``.  Positions do
-    not enter the scores.  Returns [T, heads * dv]."""
+    not enter the scores unless ``slopes`` is given.  On its way to the softmax a score ``(q . k) * scale`` is
+    multiplied by ``head_scale[h]`` (float32 [heads]), capped as ``softcap * tanh(s / softcap)`` (``softcap`` 0: not),
+    and lowered by ``slopes[h] * (i - j)`` (float32 [heads]); the result is multiplied by ``out_scale``.
+    Returns [T, heads * dv]."""
     _need_cuda(q, pages)
     assert q.stride(1) == 1 and pages.is_contiguous() and pages.dtype == q.dtype
     T = q.shape[0]
     out = new((T, heads * dv), q.dtype, q.device)
+    if head_scale is not None or slopes is not None or softcap or out_scale != 1.0:
+        for v in (head_scale, slopes):
+            assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
+        rc = lib("window_attention").kvb_window_attention_shaped(
+            c_void_p(_at(q, q_off)), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+            c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions), _p(batch.token_req), _p(out), c_int(T),
+            c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_float(scale), c_int(int(window or 0)),
+            c_int(int(keep_first or 0)), c_int(1 if one_more else 0), _p(head_scale), _p(slopes), c_float(float(softcap or 0.0)),
+            c_float(float(out_scale)), c_int(dtype_code(q.dtype)), _p(batch.status), _stream())
+        _check(rc, "window_attention")
+        choices["window_attention"] += 1
+        choices["window_attention_shaped"] += 1
+        return out
     rc = lib("window_attention").kvb_window_attention(
         c_void_p(_at(q, q_off)), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]),
         c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions), _p(batch.token_req), _p(out), c_int(T),
@@ -737,6 +760,274 @@ def flash_attention_rows(q: torch.Tensor, pages: torch.Tensor, block_table, batc
     _check(rc, "flash_attention_rows")
     choices["flash_attention_rows"] += 1
     choices[f"flash_attention_rows_{wide}"] += 1
+    return out
+
+
+def qk_norm_append(p: torch.Tensor, first: int, k_off: int, v_off: int, bq, bk, bv, qw, kw, eps: float, pages: torch.Tensor,
+                   block_table, batch, heads: int, kv_heads: int, dk: int, dv: int, write: bool = True) -> torch.Tensor:
+    """What lies between the q|k|v product and an attention over [key | value] rows: the biases (float32, each may
+    be None) join their projections, every query and key head is divided by its root mean square (eps inside the
+    root) and multiplied by a weight of ``dk`` shared by the heads (``qw``, ``kw``; None: no norm), the keys and
+    values go into the requests' pages.  ``p`` [T, *]: queries from column ``first``, keys ``k_off`` columns further,
+    values ``v_off`` columns further.  Returns the queries [T, heads * dk]."""
+    _need_cuda(p, pages)
+    assert p.stride(1) == 1 and pages.is_contiguous() and pages.dtype == p.dtype
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
+    for v, n in ((bq, heads * dk), (bk, kv_heads * dk), (bv, kv_heads * dv), (qw, dk), (kw, dk)):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n)
+    T = p.shape[0]
+    q = new((T, heads * dk), p.dtype, p.device)
+    rc = lib("window_attention").kvb_qk_norm_append(
+        c_void_p(_at(p, first)), c_int(p.stride(0)), c_int(k_off), c_int(v_off), _p(bq), _p(bk), _p(bv), _p(qw), _p(kw),
+        c_float(eps), _p(q),
+        _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]), c_int(pages.shape[0]),
+        _p(batch.positions), _p(batch.token_req), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+        c_int(1 if write else 0), c_int(dtype_code(p.dtype)), _p(batch.status), _stream())
+    _check(rc, "qk_norm_append")
+    return q
+
+
+# ------------------------------------------------------------------ several residual streams, token shift, xIELU
+
+class _HyperArgs(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("y2", c_void_p), ("mix", c_void_p), ("out_w", c_void_p),
+                ("in_w", c_void_p), ("weight", c_void_p), ("rows", c_void_p), ("out", c_void_p), ("n", c_int), ("S", c_int),
+                ("W", c_int), ("eps", c_float), ("one_plus", c_int), ("out_f32", c_int), ("shift", c_void_p),
+                ("shift_state", c_void_p), ("slot_stride", c_longlong), ("slots", c_void_p), ("positions", c_void_p),
+                ("prev", c_void_p), ("token_req", c_void_p), ("q_start", c_void_p)]
+
+
+class PendingStreams:
+    """A sublayer's output that has not been written into the residual streams yet: up to two tensors ``ys`` [T, W]
+    of the compute type (two mixers that ran side by side hand on both), the mixing matrix ``mix`` [S, S] (indexed
+    [from, to]) and the weights ``out_w`` [S] of the write  x_t <- sum_s mix[s, t] x_s + out_w[t] * sum(ys).
+    :func:`hyper_norm` carries it out in the kernel that also makes the next sublayer's input."""
+    __slots__ = ("ys", "mix", "out_w")
+
+    def __init__(self, ys, mix, out_w):
+        self.ys = tuple(y for y in ys if y is not None)
+        assert 1 <= len(self.ys) <= 2
+        self.mix, self.out_w = mix, out_w
+
+
+def embed_sinusoid_streams(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, streams: int,
+                           status: torch.Tensor, sampled: Optional[torch.Tensor] = None,
+                           base: float = 10000.0) -> torch.Tensor:
+    """float32 [T, streams, W]: ``table[ids]`` plus the sinusoidal vector of each token's position (entry 2i:
+    ``sin(p base^(-2i / W))``, entry 2i + 1 the cosine of the same angle), the same row in every stream.  Ids below
+    zero name tokens still on the device, as for :func:`embed_gather`."""
+    _need_cuda(table, ids, sampled)
+    V, W = table.shape
+    T = ids.numel()
+    out = new((T, streams, W), torch.float32, table.device)
+    rc = lib("streams").kvb_embed_sinusoid_streams(
+        _p(table), dtype_code(table.dtype), _p(ids), _p(sampled), c_int(0 if sampled is None else sampled.numel()),
+        _p(positions), _p(out), c_int(T), c_int(streams), c_int(W), c_int(V), c_float(base), _p(status), _stream())
+    _check(rc, "embed_sinusoid_streams")
+    return out
+
+
+def hyper_norm(x: torch.Tensor, pending: Optional[PendingStreams], in_w: Optional[torch.Tensor],
+               weight: Optional[torch.Tensor], eps: float, one_plus: bool, out_dtype: Optional[torch.dtype],
+               compute_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+               shift_state: Optional[torch.Tensor] = None, batch=None, stage_prev: bool = False):
+    """One launch around the residual streams ``x`` (float32 [T, S, W], updated in place unless ``rows`` selects):
+    the pending write of the sublayer before, the read ``u = sum_s in_w[s] x_s`` (``in_w`` None: the plain sum) and
+    its RMS norm times ``weight`` (``one_plus``: times 1 + weight).  ``out_dtype`` None: only the write.
+    With ``shift`` (float32 [W]) and a step in which every request brings one token, the token shift follows in the
+    same launch: ``h + (h_before - h) * shift`` with ``h_before`` from ``shift_state[slot]`` (zero at position 0),
+    which then takes the unshifted row.  ``stage_prev``: for steps with runs of tokens; the row in front of every
+    run's first token is copied out of the slots and returned as the second result, for :func:`token_shift`."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3
+    T, S, W = x.shape
+    a = _HyperArgs()
+    a.x = x.data_ptr()
+    if pending is not None:
+        for i, y in enumerate(pending.ys):
+            assert y.shape == (T, W) and y.is_contiguous() and y.dtype == compute_dtype
+            setattr(a, "y" if i == 0 else "y2", y.data_ptr())
+        for v, n in ((pending.mix, S * S), (pending.out_w, S)):
+            assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n)
+        a.mix = 0 if pending.mix is None else pending.mix.data_ptr()
+        a.out_w = 0 if pending.out_w is None else pending.out_w.data_ptr()
+    for v, n in ((in_w, S), (weight, W), (shift, W)):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n)
+    a.in_w = 0 if in_w is None else in_w.data_ptr()
+    a.weight = 0 if weight is None else weight.data_ptr()
+    n = T if rows is None else rows.numel()
+    a.rows = 0 if rows is None else rows.data_ptr()
+    out = prev = None
+    if out_dtype is not None:
+        out = new((n, W), out_dtype, x.device)
+        a.out = out.data_ptr()
+    a.n, a.S, a.W, a.eps, a.one_plus = n, S, W, eps, 1 if one_plus else 0
+    a.out_f32 = 1 if out_dtype == torch.float32 else 0
+    if shift is not None or stage_prev:
+        assert rows is None and shift_state is not None and shift_state.dtype == torch.float32 and shift_state.stride(1) == 1
+        a.shift_state, a.slot_stride = shift_state.data_ptr(), shift_state.stride(0)
+        a.slots, a.positions = batch.slots.data_ptr(), batch.positions.data_ptr()
+        if stage_prev:
+            prev = new((batch.num_reqs, W), torch.float32, x.device)
+            a.prev, a.token_req, a.q_start = prev.data_ptr(), batch.token_req.data_ptr(), batch.q_start.data_ptr()
+        else:
+            assert batch.num_reqs == T
+            a.shift = shift.data_ptr()
+    rc = lib("streams").kvb_hyper_norm(ctypes.byref(a), c_int(dtype_code(compute_dtype)), _stream())
+    _check(rc, "hyper_norm")
+    return (out, prev) if stage_prev else out
+
+
+def token_shift(h: torch.Tensor, prev: torch.Tensor, shift: torch.Tensor, state: torch.Tensor, batch,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """``h[t] + (h[t - 1] - h[t]) * shift`` along each request's run of tokens (``h`` float32 [T, W]); the row in front
+    of a run's first token is ``prev[request]``; the run's last row goes to ``state[slot]``."""
+    _need_cuda(h, prev, state)
+    assert h.dtype == torch.float32 and h.is_contiguous() and prev.is_contiguous() and state.stride(1) == 1
+    T, W = h.shape
+    out = new((T, W), out_dtype, h.device)
+    rc = lib("streams").kvb_token_shift(_p(h), _p(prev), _p(shift), _p(state), c_longlong(state.stride(0)), _p(batch.slots),
+                                        _p(batch.token_req), _p(batch.q_start), _p(out), c_int(T), c_int(W),
+                                        c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "token_shift")
+    return out
+
+
+def xielu(x: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """``z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` with ``pq`` = (p, q),
+    float32 on the device."""
+    _need_cuda(x, pq)
+    assert x.is_contiguous() and pq.dtype == torch.float32 and pq.numel() == 2
+    out = new(tuple(x.shape), x.dtype, x.device)
+    rc = lib("streams").kvb_xielu(_p(x), _p(out), c_longlong(x.numel()), _p(pq), c_int(dtype_code(x.dtype)), _stream())
+    _check(rc, "xielu")
+    return out
+
+
+# ------------------------------------------------------------------ linear recurrences with a decay per token
+
+GATE_SUMS_LIBRARY_MIN_ROWS = int(os.environ.get('KVB200_GATE_SUMS_LIBRARY_MIN_ROWS', '128'))
+
+
+def gate_coeffs(u: torch.Tensor, w: torch.Tensor, br: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
+                decay_scale: float):
+    """The coefficients of a gated diagonal recurrence.  ``u`` [T, C]; ``w`` [blocks, 2 bw, bw] of the compute type,
+    block b's rows 0 .. bw-1 making the decay gate r and the rest the input gate i from ``u``'s block b; ``br``, ``bi``,
+    ``lam`` float32 [C].  Returns float32 ``a = exp(-decay_scale r softplus(lam))`` and ``b = sqrt(1 - a^2) i u``,
+    both [T, C].  The gates' sums are float32 (this package's FMA kernel; for bfloat16 steps of many rows the
+    library's batched product with float32 output)."""
+    _need_cuda(u, w)
+    nb, two_bw, bw = w.shape
+    assert two_bw == 2 * bw and u.shape[1] == nb * bw and u.stride(1) == 1 and w.is_contiguous() and w.dtype == u.dtype
+    T, C = u.shape
+    a = new((T, C), torch.float32, u.device)
+    b = new((T, C), torch.float32, u.device)
+    if u.dtype == torch.bfloat16 and T >= GATE_SUMS_LIBRARY_MIN_ROWS and _bmm_f32_ok():
+        pre = new((nb, T, 2 * bw), torch.float32, u.device)
+        uv = torch.as_strided(u, (nb, T, bw), (bw, u.stride(0), 1), u.storage_offset())
+        torch.bmm(uv, w.transpose(1, 2), out_dtype=torch.float32, out=pre)
+        if _marks is not None:
+            _mark("gate_sums_library")
+        choices["gate_sums_library"] += 1
+        rc = lib("recurrence").kvb_coeffs_from_sums(_p(pre), _p(u), c_int(u.stride(0)), _p(br), _p(bi), _p(lam),
+                                                    c_float(decay_scale), _p(a), _p(b), c_int(T), c_int(nb), c_int(bw),
+                                                    c_int(dtype_code(u.dtype)), _stream())
+        _check(rc, "coeffs_from_sums")
+        return a, b
+    rc = lib("recurrence").kvb_gate_coeffs(_p(u), c_int(u.stride(0)), _p(w), _p(br), _p(bi), _p(lam), c_float(decay_scale),
+                                           _p(a), _p(b), c_int(T), c_int(nb), c_int(bw), c_int(dtype_code(u.dtype)), _stream())
+    _check(rc, "gate_coeffs")
+    return a, b
+
+
+_bmm_f32: Optional[bool] = None
+
+
+def _bmm_f32_ok() -> bool:
+    """Whether the library's batched product writes float32 from bfloat16 operands (asked once, on tiny tensors)."""
+    global _bmm_f32
+    if _bmm_f32 is None:
+        if _capturing():
+            return False
+        try:
+            x = torch.zeros((1, 8, 8), dtype=torch.bfloat16, device="cuda")
+            torch.bmm(x, x, out_dtype=torch.float32, out=torch.empty((1, 8, 8), dtype=torch.float32, device="cuda"))
+            _bmm_f32 = True
+        except (TypeError, RuntimeError, NotImplementedError):
+            _bmm_f32 = False
+    return _bmm_f32
+
+
+class _DiagArgs(ctypes.Structure):
+    _fields_ = [("a", c_void_p), ("b", c_void_p), ("y", c_void_p), ("ld_y", c_int), ("y_bias", c_void_p),
+                ("out_scale", c_float), ("out", c_void_p), ("state", c_void_p), ("slot_stride", c_longlong),
+                ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("C", c_int)]
+
+
+def diag_scan(a: torch.Tensor, b: torch.Tensor, y, y_bias: Optional[torch.Tensor], out_scale: float,
+              state: torch.Tensor, batch, out_dtype: torch.dtype) -> torch.Tensor:
+    """``S_t = a_t S_{t-1} + b_t`` per channel along every request's tokens of the step, from the state in the
+    request's slot (zero for a request that starts at position 0), which is left up to date.  ``y``: (tensor,
+    first column) of the gate branch [T, C] before its activation.  Returns
+    ``S_t * gelu_tanh(y_t + y_bias) * out_scale`` [T, C]."""
+    _need_cuda(a, b, state)
+    T, C = a.shape
+    yt, ycol = y
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+    assert yt.dtype == out_dtype and yt.stride(1) == 1 and state.dtype == torch.float32 and state.stride(1) == 1
+    out = new((T, C), out_dtype, a.device)
+    p = _DiagArgs(a.data_ptr(), b.data_ptr(), _at(yt, ycol), yt.stride(0), 0 if y_bias is None else y_bias.data_ptr(),
+                  float(out_scale), out.data_ptr(), state.data_ptr(), state.stride(0), batch.q_start.data_ptr(),
+                  batch.req_start.data_ptr(), batch.slots.data_ptr(), C)
+    rc = lib("recurrence").kvb_diag_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "diag_scan")
+    return out
+
+
+class _SsdArgs(ctypes.Structure):
+    _fields_ = [("xbc", c_void_p), ("ld_xbc", c_int), ("dt", c_void_p), ("ld_dt", c_int), ("dt_bias", c_void_p),
+                ("A_log", c_void_p), ("D", c_void_p), ("state", c_void_p), ("slot_stride", c_longlong), ("y", c_void_p),
+                ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int),
+                ("N", c_int), ("Dv", c_int), ("cols", c_int)]
+
+
+def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, batch, heads: int, groups: int, n: int, dv: int) -> torch.Tensor:
+    """A matrix state ``S`` [n, dv] per head with one decay per head and token, along every request's tokens of the
+    step:  ``dt = softplus(dt_raw + dt_bias)``, ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D x``.
+    ``xbc`` [T, heads dv + 2 groups n]: x | B | C (head h reads group ``h // (heads / groups)``); ``dt``: (tensor, first
+    column) of the raw step sizes [T, heads].  ``state``: float32 [slots, >= heads * dv * n], zero for a request
+    that starts at position 0.  Returns float32 y [T, heads * dv]."""
+    _need_cuda(xbc, state)
+    T = xbc.shape[0]
+    dtt, dcol = dt
+    assert xbc.stride(1) == 1 and dtt.stride(1) == 1 and dtt.dtype == xbc.dtype and state.dtype == torch.float32
+    assert state.stride(1) == 1 and xbc.shape[1] >= heads * dv + 2 * groups * n
+    for v in (dt_bias, a_log, d_skip):
+        assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
+    y = new((T, heads * dv), torch.float32, xbc.device)
+    p = _SsdArgs(xbc.data_ptr(), xbc.stride(0), _at(dtt, dcol), dtt.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
+                 d_skip.data_ptr(), state.data_ptr(), state.stride(0), y.data_ptr(), batch.q_start.data_ptr(),
+                 batch.req_start.data_ptr(), batch.slots.data_ptr(), heads, groups, n, dv, 0)
+    rc = lib("recurrence").kvb_ssd_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(dtype_code(xbc.dtype)), _stream())
+    _check(rc, "ssd_scan")
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, z, weight: torch.Tensor, groups: int, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """``v = y * silu(z)``, then each of ``groups`` equal parts of a row divided by its own root mean square (eps
+    inside the root), times ``weight``.  ``y`` float32 [T, width]; ``z``: (tensor, first column), compute type."""
+    _need_cuda(y, weight)
+    T, width = y.shape
+    zt, zcol = z
+    assert y.dtype == torch.float32 and y.is_contiguous() and zt.stride(1) == 1 and zt.dtype == out_dtype
+    assert weight.dtype == torch.float32 and weight.numel() == width
+    out = new((T, width), out_dtype, y.device)
+    rc = lib("recurrence").kvb_gated_group_norm(_p(y), c_void_p(_at(zt, zcol)), c_int(zt.stride(0)), _p(weight), _p(out),
+                                                c_int(T), c_int(width), c_int(groups), c_float(eps),
+                                                c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "gated_group_norm")
     return out
 
 

@@ -75,3 +75,23 @@ class LinearHead(Part):
     def forward(self, x):
         import torch
         return ops.linear(x, self.weight, out_dtype=torch.float32)
+
+
+@register("embedding", "sinusoid_stream_embedding")
+class SinusoidStreamEmbedding(TokenEmbedding):
+    """``x[t] = table[token[t]] + pe(position[t])`` with the sinusoidal vector ``pe(p)[2i] = sin(p base^(-2i / W))``,
+    ``pe(p)[2i + 1] = cos`` of the same angle, copied into ``streams`` residual streams: float32 [T, streams, W].
+    params: vocab_size, hidden_size, streams, base."""
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("streams",)
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.stream_copies = int(params.get("streams", 1))
+        self.base = float(params.get("base", 10000.0))
+
+    def forward(self, batch):
+        return ops.embed_sinusoid_streams(self.table, batch.token_ids, batch.positions, self.stream_copies, batch.status,
+                                          batch.sampled, self.base)

@@ -106,3 +106,29 @@ class GatedDense(Part):
         if self.down_bias is not None:
             y = y + self.down_bias.to(y.dtype)
         return y
+
+
+@register("feed_forward", "dense_xielu")
+class DenseXIELU(Part):
+    """``down( act(up(x)) )`` without gate or bias, ``act`` the xIELU with two learned numbers (p, q):
+    ``z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``.
+    params: hidden_size, intermediate_size."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, i = int(params["hidden_size"]), int(params["intermediate_size"])
+        return {"up": WeightSpec((i, h)), "down": WeightSpec((h, i)), "act": WeightSpec((2,), "bias")}
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("streams",) + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.up, self.down, self.act = weights["up"], weights["down"], weights["act"]
+
+    def activation_widths(self):
+        return [self.up.shape[0], self.up.shape[0], self.down.shape[0]]
+
+    def forward(self, x, batch):
+        return ops.linear(ops.xielu(ops.linear(x, self.up), self.act), self.down)

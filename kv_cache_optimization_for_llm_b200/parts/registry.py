@@ -35,5 +35,5 @@ def known(family: str):
 
 
 def _load_builtin() -> None:
-    from . import (attention, block, delta_rule, embedding, experts, feed_forward, latent_attention, norm,  # noqa: F401
-                   position, stream, window_attention)
+    from . import (attention, block, delta_rule, embedding, experts, feed_forward, hyper, latent_attention, norm,  # noqa: F401
+                   position, recurrence, stream, window_attention)

@@ -1,12 +1,16 @@
-"""Attention whose mask is a sliding window that keeps the sequence's first tokens, over
-queries, keys and values that pass a short convolution first."""
+"""Attention over a sliding window with one row [key | value] per token and key/value head in the pages: one whose
+queries, keys and values pass a short convolution first and whose window keeps the sequence's first tokens; one
+whose scores are shaped on their way to the softmax (a factor per head, a soft cap, a bias that grows with the
+distance); and the arrangement of two mixers side by side."""
 
 from __future__ import annotations
+
+import dataclasses
 
 import torch
 
 from .. import ops
-from ..cache.specs import PagedKVSpec, PagedWithStateSpec, SlotStateSpec
+from ..cache.specs import PagedKVSpec, PagedWithStateSpec, SlotStateSpec, paged_part, state_part
 from ..weights.loader import WeightSpec
 from .base import Part
 from .registry import register
@@ -101,3 +105,172 @@ class ConvWindowAttention(Part):
             a = ops.window_attention(c, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
                                      self.scale, self.window or 0, self.keep_first, self.one_more)
         return ops.linear(a, self.o)
+
+
+@register("mixer", "shaped_window_attention")
+class ShapedWindowAttention(Part):
+    """Grouped-query attention whose scores are shaped on their way to the softmax, over a sliding window.
+
+    q (``heads`` x ``dim``), k (``kv_heads`` x ``dim``) and v (``kv_heads`` x ``vdim``) come from one product with the
+    row-stacked matrix; with ``bias`` each gets a bias; with ``qk_norm`` every query and key head is divided by its
+    root mean square (eps inside the root) and multiplied by a weight of ``dim`` shared by the heads.  Keys and values
+    go to the request's pages, a row [k | v] per token and key/value head.  No rotation.  For query i and key j
+
+        s = (q . k) * scale * temp[h];    s <- softcap * tanh(s / softcap);    s <- s - slope_h * (i - j),
+
+    with ``temp`` a learned number per head (``head_temperature``), ``softcap`` 0 or None for no cap, and
+    ``slope_h = 2^(-slope_power * (h + 1) / heads)`` (``slope_power`` None: no distance bias).  Query i sees key j when
+    ``0 <= i - j < window`` (``window`` None: every key up to i).  Ordinary softmax, float32.  ``out_scale`` multiplies
+    the result.  Then W_o.
+    params: hidden_size, heads, kv_heads, dim, vdim, scale, window, softcap, slope_power, bias, qk_norm,
+    head_temperature, eps, out_scale."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, H, G, D, Dv = (int(params[k]) for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim"))
+        specs = {"q": WeightSpec((H * D, h)), "k": WeightSpec((G * D, h)), "v": WeightSpec((G * Dv, h)),
+                 "o": WeightSpec((h, H * Dv))}
+        if params.get("bias"):
+            specs.update(q_bias=WeightSpec((H * D,), "bias"), k_bias=WeightSpec((G * D,), "bias"),
+                         v_bias=WeightSpec((G * Dv,), "bias"))
+        if params.get("qk_norm"):
+            specs.update(q_norm=WeightSpec((D,), "vector"), k_norm=WeightSpec((D,), "vector"))
+        if params.get("head_temperature"):
+            specs["temp"] = WeightSpec((H,), "bias")
+        return specs
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("window_attention",) + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.heads, self.kv_heads = int(params["heads"]), int(params["kv_heads"])
+        self.dim, self.vdim = int(params["dim"]), int(params["vdim"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"shaped_window_attention: {self.heads} query heads cannot be grouped over "
+                             f"{self.kv_heads} key/value heads")
+        if not (1 <= self.dim <= 256 and 1 <= self.vdim <= 256):
+            raise ValueError(f"shaped_window_attention: head sizes {self.dim} x {self.vdim} are refused (1 to 256)")
+        self.scale, self.eps = float(params["scale"]), float(params.get("eps", 1e-6))
+        self.window = int(params["window"]) if params.get("window") else None
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.out_scale = float(params.get("out_scale", 1.0))
+        self.w_in, (_, self.k_off, self.v_off) = _stack_rows([weights["q"], weights["k"], weights["v"]])
+        self.q_bias, self.k_bias, self.v_bias = (weights.get(n) for n in ("q_bias", "k_bias", "v_bias"))
+        self.q_norm, self.k_norm = weights.get("q_norm"), weights.get("k_norm")
+        self.temp = weights.get("temp")
+        self.slopes = None
+        if params.get("slope_power") is not None:
+            power = float(params["slope_power"])
+            self.slopes = torch.tensor([2.0 ** (-power * (h + 1) / self.heads) for h in range(self.heads)],
+                                       dtype=torch.float32, device=ctx.device)
+        self.o = weights["o"]
+
+    def cache_spec(self):
+        return PagedKVSpec(self.kv_heads, self.dim + self.vdim, self.window, planes=1)
+
+    def activation_widths(self):
+        return [self.w_in.shape[0], self.heads * self.dim, self.heads * self.vdim, self.o.shape[0]]
+
+    def readout(self, p, first, batch, cache):
+        """From the product ``p`` (this mixer's columns start at ``first``) to the heads' results [T, heads * vdim]."""
+        table = batch.block_tables[cache.group]
+        q = ops.qk_norm_append(p, first, self.k_off, self.v_off, self.q_bias, self.k_bias, self.v_bias, self.q_norm,
+                               self.k_norm, self.eps, cache.k, table, batch, self.heads, self.kv_heads, self.dim,
+                               self.vdim, write=cache.write)
+        return ops.window_attention(q, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                    self.scale, self.window or 0, 0, False, head_scale=self.temp, slopes=self.slopes,
+                                    softcap=self.softcap, out_scale=self.out_scale)
+
+    def forward(self, x, batch, cache):
+        return ops.linear(self.readout(ops.linear(x, self.w_in), 0, batch, cache), self.o)
+
+
+def _stack_rows(mats):
+    """Row-stacks matrices [n_i, in], each starting on a multiple of 8 rows; returns the matrix and the starts."""
+    starts, rows, at = [], [], 0
+    for m in mats:
+        starts.append(at)
+        rows.append(m)
+        pad = -m.shape[0] % 8
+        if pad:
+            rows.append(torch.zeros((pad, m.shape[1]), dtype=m.dtype, device=m.device))
+        at += m.shape[0] + pad
+    return torch.cat(rows, dim=0).contiguous(), starts
+
+
+@register("mixer", "side_by_side")
+class SideBySide(Part):
+    """Two mixers that read the same input and whose results are summed: ``left_scale * left(h) + right_scale * right(h)``.
+    Each side is a mixer part with a stacked input matrix ``w_in``, a ``readout(product, first column, batch, cache)``
+    and an output matrix ``o``; the weights of the sum are handed to the sides as their ``out_scale``.  One product
+    with both input matrices stacked feeds both sides; the two output products are handed on together and summed by
+    whoever adds them to the residual stream.  A side's pages and state slot are the layer's: at most one side
+    keeps pages, and the sides' states lie one behind the other in the request's slot.
+    params: left, right (mixer parts)."""
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ()
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.sides = [ctx.make("mixer", params["left"]), ctx.make("mixer", params["right"])]
+        for s in self.sides:
+            if not (hasattr(s, "readout") and hasattr(s, "w_in") and hasattr(s, "o")):
+                raise ValueError(f"side_by_side: a mixer of kind {s.kind!r} cannot stand beside another "
+                                 "(it needs w_in, readout and o)")
+        self.w_in, self.starts = _stack_rows([s.w_in for s in self.sides])
+        wishes = [s.cache_spec() for s in self.sides]
+        paged = [paged_part(w) for w in wishes]
+        if sum(p is not None for p in paged) > 1:
+            raise ValueError("side_by_side: only one of the two mixers may keep pages")
+        self.paged = next((p for p in paged if p is not None), None)
+        self.floats = []
+        for w in wishes:
+            st = state_part(w)
+            if st is not None and st.dtype != torch.float32:
+                raise ValueError("side_by_side: the mixers' states must be float32 to share a slot")
+            n = 0
+            if st is not None:
+                n = 1
+                for d in st.shape:
+                    n *= int(d)
+            self.floats.append(n)
+        self._views = {}
+
+    def cache_spec(self):
+        total = sum(self.floats)
+        state = SlotStateSpec((total,), torch.float32) if total else None
+        if self.paged is not None:
+            return PagedWithStateSpec(self.paged, state) if state is not None else self.paged
+        return state
+
+    def activation_widths(self):
+        own = [self.w_in.shape[0]]
+        for s in self.sides:
+            own += list(s.activation_widths())[1:]
+        return own
+
+    def _bindings(self, cache):
+        """Each side's view of the layer's binding: the pages as they are, its own part of the state slot."""
+        state = getattr(cache, "state", None)
+        if state is None or not any(self.floats):
+            return [cache, cache]
+        got = self._views.get(id(state))
+        if got is None or got[0] is not state:
+            at, views = 0, []
+            for n in self.floats:
+                views.append(state[:, at:at + n] if n else None)
+                at += n
+            got = (state, views)
+            self._views[id(state)] = got
+        return [dataclasses.replace(cache, state=v) for v in got[1]]
+
+    def forward(self, x, batch, cache):
+        p = ops.linear(x, self.w_in)
+        outs = []
+        for side, first, binding in zip(self.sides, self.starts, self._bindings(cache)):
+            outs.append(ops.linear(side.readout(p, first, batch, binding), side.o))
+        return tuple(outs)
