@@ -28,11 +28,12 @@ class LogitRecorder:
 
         runner.run = run
 
-    def compare(self, sequences, plain_logits, limit, what=""):
+    def compare(self, sequences, plain_logits, limit, what="", err=None):
         """``sequences``: request id -> its whole token sequence (prompt and output);
         ``plain_logits(request id)`` -> [len, vocab] of the plain implementation on that
         sequence.  Every recorded row whose position lies inside the sequence must agree
-        within ``limit`` of the sequence's largest logit.  Returns (rows compared, worst)."""
+        within ``limit`` of the sequence's largest logit, or, with ``err(got row, plain row)`` given, have an error by
+        that measure below ``limit``.  Returns (rows compared, worst)."""
         refs, worst, n = {}, 0.0, 0
         for rid, pos, kept, i in self.rows:
             seq = sequences.get(rid)
@@ -42,8 +43,8 @@ class LogitRecorder:
                 refs[rid] = plain_logits(rid)
             ref = refs[rid]
             got = kept[i].float().cpu().numpy().astype(np.float64)
-            err = np.abs(got - ref[pos]).max() / np.abs(ref).max()
-            assert err < limit, f"{what}: request {rid}, position {pos}: relative error {err:.3e} (limit {limit:.0e})"
-            worst = max(worst, err)
+            e = err(got, ref[pos]) if err is not None else np.abs(got - ref[pos]).max() / np.abs(ref).max()
+            assert e < limit, f"{what}: request {rid}, position {pos}: relative error {e:.3e} (limit {limit:.0e})"
+            worst = max(worst, e)
             n += 1
         return n, worst

@@ -231,3 +231,23 @@ def test_whole_model_is_causal_and_a_prefix_gives_the_same_rows():
     other[20] = (other[20] + 1) % cfg["vocab"]
     changed = S.forward(cfg, w, other)
     assert np.allclose(changed[:20], full[:20]) and not np.allclose(changed[20], full[20])
+
+
+def _rms(got, ref):
+    return np.sqrt(((got - ref) ** 2).mean()) / np.sqrt((ref ** 2).mean())
+
+
+def test_a_lost_shift_row_or_state_would_show():
+    """The plain model itself, with one mechanism's memory cut at a step's border, differs from the whole by far more
+    than the tests' tolerance: the comparisons above can see such a fault."""
+    cfg = tiny.MIXED
+    w = {k: v.float().numpy().astype(np.float64) for k, v in tiny.draw_weights(cfg, seed=1).items()}
+    seq = np.random.default_rng(5).integers(0, cfg["vocab"], 40).tolist()
+    ref = S.forward(cfg, w, seq)
+    no_shift = dict(w)
+    for i in range(len(cfg["layers"])):
+        no_shift[f"l{i}.shift"] = np.zeros_like(w[f"l{i}.shift"])
+    assert _rms(S.forward(cfg, no_shift, seq), ref) > 0.09
+    swapped = dict(w)
+    swapped["l1.hc1.mix"] = w["l1.hc1.mix"].T.copy()
+    assert _rms(S.forward(cfg, swapped, seq), ref) > 0.09
