@@ -422,7 +422,7 @@ def rezusun_config(z):
             "max_position_embeddings": CONTEXT_LEN}
 
 
-def solulix_config(z, window=1024, keep_first=64):
+def solulix_config(z, window=1024, keep_first=64, experts=True):
     """Six layers at the comparison's sizes: attention (heads of 64, a quarter as many key/value heads, four taps, a
     window of 1024 tokens that keeps the first 64) and the gated delta rule (heads of 64 x 64) in turn; dense
     feed-forwards of the same width as Llama's, and on every third layer 32 experts of a sixteenth of that width of
@@ -433,9 +433,28 @@ def solulix_config(z, window=1024, keep_first=64):
     att = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
            "mask": {"size": window, "keep_first": keep_first}}
     dlt = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4}
-    kinds = [("attention", att, dense), ("attention", att, moe), ("delta", dlt, dense)]
+    kinds = [("attention", att, dense), ("attention", att, moe if experts else dense), ("delta", dlt, dense)]
     return {"architecture": "Solulix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
             "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": kinds[i % 3][2]} for i in range(z["layers"])],
+            "max_position_embeddings": CONTEXT_LEN}
+
+
+def nonetar_config(z, window=1024, streams=4):
+    """Six layers at the comparison's sizes: two layers of windowed attention (heads of 128 for the scores and 64 for
+    the values, a quarter as many key/value heads, a window of 1024 tokens, capped scores) beside a gated diagonal
+    recurrence as wide as the model (blocks of 64 channels, four taps), then one state-space-duality layer (twice the
+    model's width in heads of 64 with a state of 128 rows, eight groups, four taps); four residual streams; dense
+    feed-forwards of the same width as the other design's."""
+    W, H = z["width"], z["heads"]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": H, "kv_heads": H // 4, "dim": 128, "vdim": 64, "scale": 128 ** -0.5, "softcap": 30.0,
+                 "mask": {"size": window}},
+        "right": {"width": W, "blocks": W // 64, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
+    ssd = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 8,
+                                                   "norm_groups": 8, "conv": 4}}
+    return {"architecture": "Nonetar", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-6}, "streams": streams,
+            "logit_scale": 1.0, "layers": [[par, par, ssd][i % 3] for i in range(z["layers"])],
             "max_position_embeddings": CONTEXT_LEN}
 
 
@@ -584,6 +603,88 @@ def run_compare_solulix(size):
             "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
 
 
+def run_compare_nonetar(size):
+    """The Nonetar design beside Solulix (the closest design on the engine: windowed attention over [key | value]
+    rows, short convolutions, a recurrence in state slots) at equal width, depth, dense feed-forward and vocabulary."""
+    z = COMPARE_SIZES[size]
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    w0 = time.perf_counter()
+    window, keep, S = 1024, 64, 4
+    log(f"{size}: Solulix (dense feed-forwards)")
+    sol = measure_design(solulix_config(z, window, keep, experts=False))
+    log(f"{size}: Nonetar")
+    non = measure_design(nonetar_config(z, window, S))
+    w1 = time.perf_counter()
+    sampler.stop()
+    T, R, ctx = PREFILL_TOKENS, 64, PROMPT_LEN
+    seen_sol = sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(T))
+    seen = sum(min(i + 1, window) for i in range(T))
+    H, G, W = z["heads"], z["heads"] // 4, z["width"]
+    dk, dv = 128, 64
+    sol_channels = (H + 2 * G) * 64
+    C, Hs, N, Dv = W, 2 * W // 64, 128, 64
+    inner, ssd_channels = Hs * Dv, Hs * Dv + 2 * 8 * N
+
+    def per_launch(d, phase, key, *names):
+        for name in names:
+            n, ms = d[phase][key].get(name, (0, 0.0))
+            if n:
+                return ms / n
+        return None
+
+    def frac(work, ms, peak_per_s):
+        return None if not ms else round(work / (ms * 1e-3) / peak_per_s, 4)
+    tensor, hbm, fma = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9, FP32_FMA_TFLOPS_NOMINAL * 1e12
+    pre, dec = ("prefill_2048", "operators"), ("decode_b64", "operators_launched")
+    kernels = {
+        "solulix attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen_sol * 4 * H * 64, per_launch(sol, *pre, "flash_attention_rows", "window_attention"), tensor),
+        "nonetar window_attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen * 2 * H * (dk + dv), per_launch(non, *pre, "window_flash_attention", "window_attention"), tensor),
+        "solulix window_attention, batch 64 (of the measured copy peak)": frac(
+            R * min(ctx, window + keep) * 2 * G * 64 * 2, per_launch(sol, *dec, "window_attention"), hbm),
+        "nonetar window_attention, batch 64 (of the measured copy peak)": frac(
+            R * min(ctx, window) * G * (dk + dv) * 2, per_launch(non, *dec, "window_attention"), hbm),
+        # both also write the keys and values into their pages
+        "solulix conv_silu, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * sol_channels * 2, per_launch(sol, *pre, "conv_silu"), hbm),
+        "nonetar conv_silu, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * ((2 * C + ssd_channels) / 3) * 2, per_launch(non, *pre, "conv_silu"), hbm),
+        "nonetar qk_norm_append, 2048 tokens (of the measured copy peak)": frac(
+            T * ((H + G) * dk + G * dv + H * dk + G * (dk + dv)) * 2, per_launch(non, *pre, "qk_norm_append"), hbm),
+        "solulix delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * H * 64 * 64 * 10, per_launch(sol, *pre, "delta_scan"), fma),
+        "nonetar ssd_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * Hs * N * Dv * 5, per_launch(non, *pre, "ssd_scan"), fma),
+        "solulix delta_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * H * 64 * 64 * 4, per_launch(sol, *dec, "delta_scan"), hbm),
+        "nonetar ssd_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * Hs * N * Dv * 4, per_launch(non, *dec, "ssd_scan"), hbm),
+        "nonetar coeffs_from_sums, 2048 tokens (of the measured copy peak)": frac(
+            T * C * 18, per_launch(non, *pre, "coeffs_from_sums"), hbm),
+        "nonetar diag_scan, 2048 tokens (of the measured copy peak)": frac(
+            T * C * 12, per_launch(non, *pre, "diag_scan"), hbm),
+        "nonetar diag_scan, batch 64 (of the measured copy peak)": frac(
+            R * C * 20, per_launch(non, *dec, "diag_scan"), hbm),
+        "nonetar gated_group_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * inner * 8, per_launch(non, *pre, "gated_group_norm"), hbm),
+        "solulix join_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 14, per_launch(sol, *pre, "join_norm"), hbm),
+        # reads and writes every stream in float32, reads the sublayer's output, writes the next one's input
+        "nonetar hyper_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * (8 * S + 6), per_launch(non, *pre, "hyper_norm"), hbm),
+        "nonetar token_shift, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 6, per_launch(non, *pre, "token_shift"), hbm),
+        "nonetar xielu, 2048 tokens (of the measured copy peak)": frac(
+            T * z["ff"] * 4, per_launch(non, *pre, "xielu"), hbm),
+    }
+    return {"compare": size, "design": "nonetar", "beside": "solulix", "sizes": z, "window": window, "streams": S,
+            "dtype": "bf16", "data": "synthetic", "peaks": pk, "solulix": sol, "nonetar": non,
+            "kernel_roofline_fractions": kernels, "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
+
+
 def run_compare(size):
     """The Rezusun design beside Llama at equal width, depth, feed-forward and vocabulary."""
     z = COMPARE_SIZES[size]
@@ -660,12 +761,12 @@ def main():
                     help="instead of the headline: prefill and decode of another design (--design) beside a Llama model of "
                          "equal width, depth, feed-forward and vocabulary (random weights), with the time of every "
                          "operator and roofline fractions of the designs' own kernels; prints its own JSON line")
-    ap.add_argument("--design", default="rezusun", choices=["rezusun", "solulix"],
-                    help="with --compare: which design stands beside Llama")
+    ap.add_argument("--design", default="rezusun", choices=["rezusun", "solulix", "nonetar"],
+                    help="with --compare: which design stands beside Llama (nonetar: beside Solulix, the closest design)")
     args = ap.parse_args()
 
     if args.compare:
-        result = run_compare_solulix(args.compare) if args.design == "solulix" else run_compare(args.compare)
+        result = {"solulix": run_compare_solulix, "nonetar": run_compare_nonetar}.get(args.design, run_compare)(args.compare)
         print(json.dumps(result), flush=True)
         return 0
     if args.impl == "reference":

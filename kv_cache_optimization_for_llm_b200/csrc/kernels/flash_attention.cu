@@ -14,6 +14,7 @@
 // Causal limit per row: key <= position of the row's token; with a window also
 // key > position - window.
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "page_maps.cuh"
 
 #include <cuda.h>
@@ -25,35 +26,7 @@ constexpr int BN = 64;   // keys per tile
 // Query rows per block: 16 per warp.  Eight warps (128 rows) when the step has enough
 // query tiles to fill the GPU with them, four warps (64 rows) otherwise.
 
-__device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
-  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-  const int n = valid ? 16 : 0;  // src-size 0: the 16 bytes are filled with zeros, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
+using namespace kvb_mma;   // cp.async with zero fill, ldmatrix, mma.sync, pack_bf16
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile whose
 // chunks are XOR-swizzled with the row, so that the 8 rows of an 8x8 matrix fall into

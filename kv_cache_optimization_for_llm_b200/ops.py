@@ -787,6 +787,59 @@ def qk_norm_append(p: torch.Tensor, first: int, k_off: int, v_off: int, bq, bk, 
     return q
 
 
+def rows_tokens_per_tile(group: int, wide: bool) -> int:
+    """Query tokens in one tile of :func:`window_flash_attention`: 64 (``wide``: 128) rows over the group of query
+    heads padded to a power of two."""
+    gp = 1
+    while gp < group:
+        gp <<= 1
+    return max(1, (128 if wide else 64) // gp)
+
+
+def window_flash_attention_supported(dk: int, dv: int, group: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of :func:`window_attention` for steps with runs of tokens takes these sizes:
+    bfloat16, key and value sizes that are multiples of 8 up to 128, at most 64 query heads per key/value head, pages
+    of a power of two."""
+    return (dtype == torch.bfloat16 and 8 <= dk <= 128 and dk % 8 == 0 and 8 <= dv <= 128 and dv % 8 == 0
+            and 1 <= group <= 64 and page_size >= 1 and page_size & (page_size - 1) == 0)
+
+
+# Which tiles the tensor-core attention over [key | value] rows of unequal sizes cuts a step into: "" chosen from the
+# step's size (128 rows when such tiles fill the GPU twice over), "0" 64 rows, "1" 128 rows.
+WINDOW_FLASH_WIDE = {"": None, "0": False, "1": True}[os.environ.get('KVB200_WINDOW_FLASH_WIDE', '')]
+
+
+def window_flash_attention(q: torch.Tensor, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int, dk: int,
+                           dv: int, scale: float, window: int, keep_first: int, one_more: bool,
+                           head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                           softcap: float = 0.0, out_scale: float = 1.0, wide: Optional[bool] = None) -> torch.Tensor:
+    """:func:`window_attention` on tensor cores for bfloat16 steps with runs of query tokens: the same mask, softmax
+    and shaping of the scores (float32), the two products on ``mma.sync`` with the probabilities rounded to bfloat16.
+    Queries at ``q[:, : heads * dk]``; ``pages`` [num_pages, kv_heads, page_size, dk + dv].  Returns [T, heads * dv]."""
+    _need_cuda(q, pages)
+    assert q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and pages.is_contiguous() and q.stride(1) == 1
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
+    for v in (head_scale, slopes):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
+    T = q.shape[0]
+    group = heads // kv_heads
+    if wide is None:
+        wide = WINDOW_FLASH_WIDE
+    if wide is None:
+        wide = (T // rows_tokens_per_tile(group, True)) * kv_heads >= 2 * sm_count(q.device)
+    tiles = tiles_of_height(batch, rows_tokens_per_tile(group, bool(wide)))
+    out = new((T, heads * dv), q.dtype, q.device)
+    rc = lib("window_flash_attention").kvb_window_flash_attention(
+        _p(q), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]),
+        c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), c_int(1 if wide else 0), _p(out),
+        c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_float(scale), c_int(int(window or 0)),
+        c_int(int(keep_first or 0)), c_int(1 if one_more else 0), _p(head_scale), _p(slopes), c_float(float(softcap or 0.0)),
+        c_float(float(out_scale)), _p(batch.status), _stream())
+    _check(rc, "window_flash_attention")
+    choices["window_flash_attention"] += 1
+    return out
+
+
 # ------------------------------------------------------------------ several residual streams, token shift, xIELU
 
 class _HyperArgs(ctypes.Structure):
@@ -1331,7 +1384,12 @@ def flash_tiles(batch, group: int, wide: bool) -> torch.Tensor:
     """The query tiles of a step for a group size: [n, 4] int32 rows (request row, first
     token row, tokens, 0), each tile holding consecutive tokens of one request.  Built
     once per step, group size and tile height, kept on the batch."""
-    nt = flash_tokens_per_tile(group, bool(wide))
+    return tiles_of_height(batch, flash_tokens_per_tile(group, bool(wide)))
+
+
+def tiles_of_height(batch, nt: int) -> torch.Tensor:
+    """The step's runs of tokens cut into query tiles of at most ``nt`` tokens: [n, 4] int32 rows (request row, first
+    token row, tokens, 0)."""
     ready = (getattr(batch, "tiles", None) or {}).get(nt)
     if ready is not None:
         return ready            # laid out with the batch's other arrays and copied with them

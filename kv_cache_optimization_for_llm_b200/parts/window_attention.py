@@ -141,7 +141,15 @@ class ShapedWindowAttention(Part):
 
     @classmethod
     def kernel_modules(cls, params, dtype):
-        return ("window_attention",) + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
+        if dtype == torch.float32:
+            return ("window_attention", "gemm_f32")
+        flash = ("window_flash_attention",) if cls._flash_sizes(params, dtype) else ()
+        return ("window_attention",) + flash + ("gemm_bf16", "gemm_bf16_wide")
+
+    @staticmethod
+    def _flash_sizes(params, dtype, page_size=16):
+        return ops.window_flash_attention_supported(int(params["dim"]), int(params["vdim"]),
+                                                    int(params["heads"]) // max(1, int(params["kv_heads"])), page_size, dtype)
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
@@ -173,12 +181,24 @@ class ShapedWindowAttention(Part):
     def activation_widths(self):
         return [self.w_in.shape[0], self.heads * self.dim, self.heads * self.vdim, self.o.shape[0]]
 
+    def query_tile_heights(self):
+        """Tokens per tile of the tensor-core kernel for prompt portions (bfloat16, sizes that are multiples of 8 up to
+        128): the step's batch lays the tiles out for them."""
+        if not self._flash_sizes(self.params, self.ctx.dtype):
+            return []
+        g = self.heads // self.kv_heads
+        return [ops.rows_tokens_per_tile(g, False), ops.rows_tokens_per_tile(g, True)]
+
     def readout(self, p, first, batch, cache):
         """From the product ``p`` (this mixer's columns start at ``first``) to the heads' results [T, heads * vdim]."""
         table = batch.block_tables[cache.group]
         q = ops.qk_norm_append(p, first, self.k_off, self.v_off, self.q_bias, self.k_bias, self.v_bias, self.q_norm,
                                self.k_norm, self.eps, cache.k, table, batch, self.heads, self.kv_heads, self.dim,
                                self.vdim, write=cache.write)
+        if not batch.decode_only and self._flash_sizes(self.params, self.ctx.dtype, cache.page_size):
+            return ops.window_flash_attention(q, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                              self.scale, self.window or 0, 0, False, head_scale=self.temp,
+                                              slopes=self.slopes, softcap=self.softcap, out_scale=self.out_scale)
         return ops.window_attention(q, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
                                     self.scale, self.window or 0, 0, False, head_scale=self.temp, slopes=self.slopes,
                                     softcap=self.softcap, out_scale=self.out_scale)
@@ -252,6 +272,14 @@ class SideBySide(Part):
         for s in self.sides:
             own += list(s.activation_widths())[1:]
         return own
+
+    def query_tile_heights(self):
+        out = []
+        for s in self.sides:
+            fn = getattr(s, "query_tile_heights", None)
+            if fn is not None:
+                out.extend(fn())
+        return out
 
     def _bindings(self, cache):
         """Each side's view of the layer's binding: the pages as they are, its own part of the state slot."""

@@ -28,12 +28,11 @@ class LogitRecorder:
 
         runner.run = run
 
-    def compare(self, sequences, plain_logits, limit, what="", err=None):
+    def compare(self, sequences, plain_logits, limit, what=""):
         """``sequences``: request id -> its whole token sequence (prompt and output);
         ``plain_logits(request id)`` -> [len, vocab] of the plain implementation on that
         sequence.  Every recorded row whose position lies inside the sequence must agree
-        within ``limit`` of the sequence's largest logit, or, with ``err(got row, plain row)`` given, have an error by
-        that measure below ``limit``.  Returns (rows compared, worst)."""
+        within ``limit`` of the sequence's largest logit.  Returns (rows compared, worst)."""
         refs, worst, n = {}, 0.0, 0
         for rid, pos, kept, i in self.rows:
             seq = sequences.get(rid)
@@ -43,8 +42,21 @@ class LogitRecorder:
                 refs[rid] = plain_logits(rid)
             ref = refs[rid]
             got = kept[i].float().cpu().numpy().astype(np.float64)
-            e = err(got, ref[pos]) if err is not None else np.abs(got - ref[pos]).max() / np.abs(ref).max()
+            e = np.abs(got - ref[pos]).max() / np.abs(ref).max()
             assert e < limit, f"{what}: request {rid}, position {pos}: relative error {e:.3e} (limit {limit:.0e})"
             worst = max(worst, e)
             n += 1
         return n, worst
+
+    def collect(self, sequences):
+        """request id -> (positions, recorded rows [n, vocab] as float64) of every recorded row whose position lies
+        inside the request's final sequence, for comparisons over all rows of a request at once."""
+        out = {}
+        for rid, pos, kept, i in self.rows:
+            seq = sequences.get(rid)
+            if seq is None or pos >= len(seq):
+                continue
+            positions, rows = out.setdefault(rid, ([], []))
+            positions.append(pos)
+            rows.append(kept[i].float().cpu().numpy().astype(np.float64))
+        return {rid: (np.asarray(ps), np.stack(rows)) for rid, (ps, rows) in out.items()}

@@ -169,7 +169,10 @@ def _left_weights(rng, H, m):
                                    dict(heads=3, kv_heads=1, dim=64, vdim=64, scale=0.125, size=33, softcap=30.0),
                                    dict(heads=1, kv_heads=1, dim=5, vdim=3, scale=1.0, size=1, softcap=2.0),
                                    dict(heads=4, kv_heads=4, dim=32, vdim=16, scale=0.3, size=None, softcap=8.0),
-                                   dict(heads=8, kv_heads=2, dim=40, vdim=24, scale=0.15, size=64, softcap=5.0)])
+                                   dict(heads=8, kv_heads=2, dim=40, vdim=24, scale=0.15, size=64, softcap=5.0),
+                                   dict(heads=4, kv_heads=2, dim=96, vdim=48, scale=0.1, size=50, softcap=20.0),
+                                   dict(heads=8, kv_heads=1, dim=128, vdim=64, scale=0.09, size=40, softcap=None),
+                                   dict(heads=2, kv_heads=1, dim=64, vdim=128, scale=0.12, size=None, softcap=3.0)])
 def test_attention_alone_in_portions_and_beside_another_request(dtype, shape):
     """Several shapes (grouped and ungrouped heads, key and value sizes that differ, a window of one token, no window,
     no cap), 70 and 33 tokens on pages of 8 that lie scattered; portions end inside pages and on their borders."""
@@ -183,7 +186,12 @@ def test_attention_alone_in_portions_and_beside_another_request(dtype, shape):
     for r, T in enumerate((70, 33)):
         x, x64 = _w(rng, (T, H), 1.0)
         xs[r], refs[r] = x.to(DT[dtype]).cuda(), 0.7 * S.capped_window_attention(x64, w64, m, 1e-5)
+    from kv_cache_optimization_for_llm_b200 import ops
+    on_tensor_cores = ops.choices["window_flash_attention"]
     whole = _run_in_steps(mixer, ctx, xs, [[(0, 70)], [(1, 33)]])
+    # bfloat16 prompt portions of sizes that are multiples of 8 run on tensor cores, everything else does not
+    took = ops.choices["window_flash_attention"] > on_tensor_cores
+    assert took == (dtype == "bfloat16" and m["dim"] % 8 == 0 and m["vdim"] % 8 == 0)
     cut = _run_in_steps(mixer, ctx, xs, [[(0, 8), (1, 1)], [(0, 9), (1, 1)], [(0, 2), (1, 30)], [(0, 1), (1, 1)],
                                          [(0, 44)], [(0, 1)], [(0, 1)], [(0, 4)]])
     one = _run_in_steps(mixer, ctx, {0: xs[1]}, [[(0, 1)]] * 33)
@@ -194,10 +202,11 @@ def test_attention_alone_in_portions_and_beside_another_request(dtype, shape):
     assert _same(one[0], whole[1], dtype), "token by token"
 
 
-def _spiked(dtype, size, T, query, key, softcap=0.0, slope=None, temp=None, page=8, D=16):
+def _spiked(dtype, size, T, query, key, softcap=0.0, slope=None, temp=None, page=8, D=16, flash=False):
     """The attention kernel alone on keys and values made so that one key decides: every query and key is small but
     the pair (query, key), whose raw score is 30; the value of key j is the unit vector j.  Returns what the query at
-    ``query`` reads, in a prompt (one portion) and decoded alone, and the plain answer."""
+    ``query`` reads, in a prompt (one portion) and decoded alone, and the plain answer.  ``flash``: the prompt on the
+    tensor-core kernel, whose values have at most 128 channels: the value of key j is then the unit vector j mod 128."""
     from kv_cache_optimization_for_llm_b200 import ops
     from kv_cache_optimization_for_llm_b200.engine.batch import BatchBuilder, StepEntry
     ctx = _ctx(dtype)
@@ -208,7 +217,9 @@ def _spiked(dtype, size, T, query, key, softcap=0.0, slope=None, temp=None, page
     q[query, 3] = 6.0
     k[key] = 0
     k[key, 3] = 5.0
-    v = np.eye(T)
+    Dv = min(T, 128) if flash else T
+    v = np.zeros((T, Dv))
+    v[np.arange(T), np.arange(T) % Dv] = 1.0
     src = torch.as_tensor(np.concatenate([q, k, v], axis=1), dtype=torch.float32).to(DT[dtype]).cuda()
     s = (q @ k.T).astype(np.float64) * (1.0 if temp is None else temp)
     if softcap:
@@ -222,7 +233,7 @@ def _spiked(dtype, size, T, query, key, softcap=0.0, slope=None, temp=None, page
     ref = (w / w.sum(axis=1, keepdims=True)) @ v
     outs = []
     for steps in ([T], [query] + [1] * (T - query)):
-        pages = torch.zeros((T // page + 2, 1, page, D + T), dtype=DT[dtype], device="cuda")
+        pages = torch.zeros((T // page + 2, 1, page, D + Dv), dtype=DT[dtype], device="cuda")
         tables = {0: list(range(T // page + 1))[::-1]}
         builder = BatchBuilder(1024, 4, [64], ctx.device, ctx.status)
         at, rows = 0, []
@@ -231,10 +242,15 @@ def _spiked(dtype, size, T, query, key, softcap=0.0, slope=None, temp=None, page
                 continue
             batch = builder.build([StepEntry(0, [0] * n, at, ())], _Manager(tables, {0: 0}))
             part = src[at:at + n].contiguous()
-            ops.kv_rows_append(part, D, 2 * D, pages, batch.block_tables[0], batch, 1, D, T)
-            got = ops.window_attention(part, 0, pages, batch.block_tables[0], batch, 1, 1, D, T, 1.0, size, 0, False,
-                                       head_scale=None if temp is None else _f32([temp]),
-                                       slopes=None if slope is None else _f32([slope]), softcap=softcap)
+            ops.kv_rows_append(part, D, 2 * D, pages, batch.block_tables[0], batch, 1, D, Dv)
+            shape = dict(head_scale=None if temp is None else _f32([temp]), slopes=None if slope is None else _f32([slope]),
+                         softcap=softcap)
+            if flash and n > 1:
+                got = ops.window_flash_attention(part, pages, batch.block_tables[0], batch, 1, 1, D, Dv, 1.0, size, 0, False,
+                                                 **shape)
+            else:
+                got = ops.window_attention(part, 0, pages, batch.block_tables[0], batch, 1, 1, D, Dv, 1.0, size, 0, False,
+                                           **shape)
             rows.append(got.float().cpu())
             at += n
         outs.append(torch.cat(rows)[query].numpy())
@@ -283,6 +299,36 @@ def test_cap_factor_and_distance_bias_decide_between_two_keys(dtype):
     assert ref[key] > 0.99 and abs(a[key] - ref[key]) < tol and abs(b[key] - ref[key]) < tol
     (a, b), ref = _spiked(dtype, 50, T, query, 70, softcap=4.0, slope=0.02)      # the nearest keys gain on the far one
     assert np.abs(a - ref).max() < tol and np.abs(b - ref).max() < tol and ref[118] > ref[71] * 2
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_prompt_portions_on_tensor_cores_see_the_same_keys_and_shape_the_scores_alike(wide, monkeypatch):
+    """The tensor-core kernel of prompt portions (tiles of 64 and of 128 query rows) on the cases above: a key that
+    stands out just inside and just outside the window, on a tile's and a page's border, far back without a window, at
+    the first token; cap, factor and distance bias deciding between two keys."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    monkeypatch.setattr(ops, "WINDOW_FLASH_WIDE", wide)
+    dtype, size, T, query = "bfloat16", 37, 250, 245
+    before = ops.choices["window_flash_attention"]
+    for key, seen in ((query - size + 1, True), (query - size, False), (0, False), (query, True), (216, True), (215, True),
+                      (192, False), (191, False), (query - 130, False)):
+        (in_prompt, _), ref = _spiked(dtype, size, T, query, key, flash=True)
+        col = key % 128
+        if seen:
+            assert in_prompt[col] > 0.99 and abs(in_prompt[col] - ref[col]) < 1e-2, (key, in_prompt[col], ref[col])
+        else:
+            assert in_prompt[col] < 0.05 and ref[col] < 0.05, (key, in_prompt[col])
+        assert np.abs(in_prompt - ref).max() < 1e-2
+    for key, query_ in ((2, 249), (0, 249), (63, 200), (64, 200), (0, 2)):     # no window; keys at a tile's border
+        (in_prompt, _), ref = _spiked(dtype, 0, 250, query_, key, flash=True)
+        assert in_prompt[key % 128] > 0.99 and np.abs(in_prompt - ref).max() < 1e-2
+    T, query, key, tol = 120, 119, 19, 2e-2
+    for kw in (dict(softcap=4.0), dict(softcap=4.0, temp=0.05), dict(softcap=4.0, slope=0.05), dict(slope=0.05)):
+        (a, _), ref = _spiked(dtype, 0, T, query, key, flash=True, **kw)
+        assert np.abs(a - ref).max() < tol, kw
+    (a, _), ref = _spiked(dtype, 50, T, query, 70, softcap=4.0, slope=0.02, flash=True)
+    assert np.abs(a - ref).max() < tol and ref[118] > ref[71] * 2
+    assert ops.choices["window_flash_attention"] >= before + 19
 
 
 # --------------------------------------------------------------------------- the two recurrences
@@ -550,9 +596,13 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(dtype):
     assert [len(o) for o in outs] == [12] * 5
     seqs = {i: prompts[i] + outs[i] for i in range(5)}
     plain = {i: S.forward(cfg, w, seqs[i]) for i in seqs}
-    # bfloat16: the root mean square of a row's differences over that of the row, the measure of this file's other tests
-    measure = None if dtype == "float32" else (lambda got, ref: _logit_err(got, ref, dtype))
-    n, worst = rec.compare(seqs, lambda i: plain[i], TOL_MODEL[dtype], "greedy generation", err=measure)
+    if dtype == "float32":
+        n, worst = rec.compare(seqs, lambda i: plain[i], TOL_MODEL[dtype], "greedy generation")
+    else:       # the measure of this file's other bfloat16 comparisons: over all of a request's rows at once
+        got = rec.collect(seqs)
+        n = sum(len(ps) for ps, _ in got.values())
+        for i, (ps, rows) in got.items():
+            assert _logit_err(rows, plain[i][ps], dtype) < TOL_MODEL[dtype], f"greedy generation: request {i}"
     assert n >= 60 and llm.engine.runner._graphs
     if dtype == "float32":
         for i in seqs:
