@@ -142,6 +142,12 @@ KVB_EXPORT int kvb_coeffs_from_sums(const float* pre, const void* u, int ld_u, c
 // ---------------------------------------------------------------- diagonal recurrence
 // One thread per (request, channel) walks the request's tokens of this step, four tokens' coefficients requested
 // at a time; the chain itself is one multiply-add per token.
+//
+// A long run is cut into chunks of kDiagChunk tokens that are walked side by side.  A first kernel reduces every
+// chunk but a run's last to the pair (A, B) with S_end = A S_begin + B and notes the run's starting state; the
+// second walks chunk k from the state that the pairs of chunks 0 .. k-1 give when applied in order, and the run's
+// last chunk leaves the state in the slot.  Request row r's chunk that begins at token row t of the step keeps its
+// pair in row (r - row_off) + t / kDiagChunk of `sum_a`, `sum_b`: rows grow with r and with t, so no two chunks share one.
 struct DiagArgs {
   const float* a; const float* b;        // [T, C]
   const void* y; int ld_y;               // [T, >= C] compute type, gate branch before its activation
@@ -151,7 +157,40 @@ struct DiagArgs {
   float* state; long long slot_stride;   // slot 0's [C]
   const int* q_start; const int* req_start; const int* slots;
   int C;
+  int chunked, row_off;                  // chunked: runs are cut; requests below row_off are single chunks
+  float* sum_a; float* sum_b; float* begin;   // chunked: [rows, C] pairs, [R, C] starting states
 };
+
+constexpr int kDiagChunk = 64;
+
+__global__ void __launch_bounds__(128) diag_chunk_pairs_kernel(DiagArgs p) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y, k = blockIdx.z;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  const int run0 = p.q_start[r], run1 = p.q_start[r + 1];
+  if (k == 0) p.begin[(size_t)r * p.C + c] = p.req_start[r] > 0 ? p.state[(size_t)p.slots[r] * p.slot_stride + c] : 0.f;
+  const int t0 = run0 + k * kDiagChunk;
+  if (t0 + kDiagChunk >= run1) return;                 // the run's last chunk (or beyond it): nobody reads its pair
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t0 + kDiagChunk; t += 4) {
+    float a[4], b[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      a[x] = p.a[(size_t)(t + x) * p.C + c];
+      b[x] = p.b[(size_t)(t + x) * p.C + c];
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      B = fmaf(a[x], B, b[x]);
+      A *= a[x];
+    }
+  }
+  const size_t row = (size_t)(r - p.row_off) + t0 / kDiagChunk;
+  p.sum_a[row * p.C + c] = A;
+  p.sum_b[row * p.C + c] = B;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(128) diag_scan_kernel(DiagArgs p) {
@@ -160,9 +199,24 @@ __global__ void __launch_bounds__(128) diag_scan_kernel(DiagArgs p) {
   const int r = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= p.C) return;
-  const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
+  int t0 = p.q_start[r], t1 = p.q_start[r + 1];
   float* st = p.state + (size_t)p.slots[r] * p.slot_stride;
-  float S = p.req_start[r] > 0 ? st[c] : 0.f;
+  float S;
+  bool last = true;
+  if (p.chunked) {
+    const int k = blockIdx.z, mine = t0 + k * kDiagChunk;
+    if (mine >= t1 && k > 0) return;
+    S = p.begin[(size_t)r * p.C + c];
+    for (int j = 0; j < k; ++j) {
+      const size_t row = (size_t)(r - p.row_off) + (t0 + j * kDiagChunk) / kDiagChunk;
+      S = fmaf(p.sum_a[row * p.C + c], S, p.sum_b[row * p.C + c]);
+    }
+    t0 = mine;
+    last = mine + kDiagChunk >= t1;
+    t1 = min(t1, mine + kDiagChunk);
+  } else {
+    S = p.req_start[r] > 0 ? st[c] : 0.f;
+  }
   const float yb = p.y_bias ? p.y_bias[c] : 0.f;
   const T* y = static_cast<const T*>(p.y);
   T* out = static_cast<T*>(p.out);
@@ -185,21 +239,38 @@ __global__ void __launch_bounds__(128) diag_scan_kernel(DiagArgs p) {
     S = fmaf(p.a[(size_t)t * p.C + c], S, p.b[(size_t)t * p.C + c]);
     out[(size_t)t * p.C + c] = from_f32<T>(S * gelu_tanh_f(to_f32(y[(size_t)t * p.ld_y + c]) + yb) * p.out_scale);
   }
-  st[c] = S;
+  if (last) st[c] = S;
 }
 
-KVB_EXPORT int kvb_diag_scan(const DiagArgs* args, int R, int dtype, cudaStream_t stream) {
+KVB_EXPORT int kvb_diag_chunk() { return kDiagChunk; }
+
+// max_run: the step's longest run (chunked launches only: the grid's third extent).
+KVB_EXPORT int kvb_diag_scan(const DiagArgs* args, int R, int max_run, int dtype, cudaStream_t stream) {
   DiagArgs p = *args;
   if (R <= 0) return 0;
   if (p.C < 1 || R > 65535) return KVB_ERR_BAD_SIZE;
-  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(diag_scan_kernel<T>, dim3((p.C + 127) / 128, R), dim3(128), 0, stream, p)));
+  dim3 grid((p.C + 127) / 128, R, 1);
+  if (p.chunked) {
+    if (!p.sum_a || !p.sum_b || !p.begin || max_run < 1) return KVB_ERR_BAD_SIZE;
+    grid.z = (max_run + kDiagChunk - 1) / kDiagChunk;
+    if (grid.z > 65535) return KVB_ERR_BAD_SIZE;
+    kvb_launch(diag_chunk_pairs_kernel, grid, dim3(128), 0, stream, p);
+  }
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(diag_scan_kernel<T>, grid, dim3(128), 0, stream, p)));
   return kvb_launch_result();
 }
 
 // ---------------------------------------------------------------- matrix state with a decay per head
 // A block owns `cols` value columns of one (request, head); four lanes share a column, lane l holding state rows
-// l, l + 4, ... (NPT of them) in registers for the whole run.  The run is walked in chunks of 16 tokens whose B, C,
+// l, l + 4, ... (NPT of them) in registers for the whole run.  The run is walked in pieces of 16 tokens whose B, C,
 // x and step sizes the block first brings into shared memory as float32.
+//
+// A long run is cut into chunks of `chunk` tokens that are walked side by side, in three launches:
+//   SSD_LOCAL   every chunk but a run's last, from a zero state: the state it ends with and the product of its decays
+//   ssd_carry   per state element, along the run's chunks in order: what each chunk begins with (S <- decay S + local)
+//   SSD_FINAL   every chunk from what it begins with, writing y; the run's last chunk leaves the state in the slot
+// Request row r's chunk that begins at token row t keeps its matrices in row (r - row_off) + t / chunk of `carry`.
+// A run of one chunk reads and writes its slot directly.
 struct SsdArgs {
   const void* xbc; int ld_xbc;           // [T, >= inner + 2 G N] compute type: x | B | C behind the convolution
   const void* dt; int ld_dt;             // [T, >= H] compute type: raw step sizes
@@ -208,19 +279,22 @@ struct SsdArgs {
   float* y;                              // [T, H * Dv] float32
   const int* q_start; const int* req_start; const int* slots;
   int H, G, N, Dv, cols;
+  int chunk, row_off;                    // chunk > 0: runs are cut; requests below row_off are single chunks
+  float* carry; float* decay;            // chunked: [rows][H][Dv][N] and [rows][H]
 };
 
-constexpr int kSsdChunk = 16;
+constexpr int kSsdPiece = 16;
+enum { SSD_WHOLE = 0, SSD_LOCAL = 1, SSD_FINAL = 2 };
 
-template <typename T, int NPT>
+template <typename T, int NPT, int MODE>
 __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
   extern __shared__ float ssm[];
   const int N = p.N, cols = p.cols;
-  float* Bs = ssm;                          // [chunk][N]
-  float* Cs = Bs + kSsdChunk * N;           // [chunk][N]
-  float* xs = Cs + kSsdChunk * N;           // [chunk][cols]
-  float* dts = xs + kSsdChunk * cols;       // [chunk]
-  float* das = dts + kSsdChunk;             // [chunk]
+  float* Bs = ssm;                          // [piece][N]
+  float* Cs = Bs + kSsdPiece * N;           // [piece][N]
+  float* xs = Cs + kSsdPiece * N;           // [piece][cols]
+  float* dts = xs + kSsdPiece * cols;       // [piece]
+  float* das = dts + kSsdPiece;             // [piece]
   pdl_trigger();
   pdl_wait();
   const int splits = (p.Dv + cols - 1) / cols;
@@ -233,26 +307,42 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
   const int pcol = tid >> 2;
   const bool owner = pcol < my_cols;
   const int pc = owner ? pcol : 0;
-  const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
-  float* st = p.state + (size_t)p.slots[r] * p.slot_stride + ((size_t)h * p.Dv + col0 + pc) * N;
-  const bool fresh = p.req_start[r] == 0;
+  int t0 = p.q_start[r], t1 = p.q_start[r + 1];
+  const size_t at = ((size_t)h * p.Dv + col0 + pc) * N;          // this thread's column within a set of matrices
+  float* st = p.state + (size_t)p.slots[r] * p.slot_stride + at;
+  const float* from = st;                   // where the state comes from, null for zeros
+  float* to = st;                           // where it goes, null for nowhere
+  if (p.req_start[r] == 0) from = nullptr;
+  size_t row = 0;
+  if (MODE != SSD_WHOLE) {
+    const int mine = t0 + (int)blockIdx.z * p.chunk;
+    const bool single = t0 + p.chunk >= t1;                      // a run of one chunk
+    if (MODE == SSD_LOCAL ? mine + p.chunk >= t1 : (mine >= t1 && blockIdx.z > 0)) return;
+    row = (size_t)(r - p.row_off) + mine / p.chunk;
+    float* mat = p.carry + row * (size_t)inner * N + at;
+    if (MODE == SSD_LOCAL) { from = nullptr; to = mat; }
+    else if (!single) { from = mat; to = mine + p.chunk >= t1 ? st : nullptr; }
+    t0 = mine;
+    t1 = min(t1, mine + p.chunk);
+  }
   float S[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = l + 4 * i;
-    S[i] = (!fresh && owner && n < N) ? st[n] : 0.f;
+    S[i] = (from && owner && n < N) ? from[n] : 0.f;
   }
   const T* xbc = static_cast<const T*>(p.xbc);
   const T* dt = static_cast<const T*>(p.dt);
   const float rate = expf(p.A_log[h]), dskip = p.D[h], dtb = p.dt_bias[h];
-  for (int c0 = t0; c0 < t1; c0 += kSsdChunk) {
-    const int nt = min(kSsdChunk, t1 - c0);
+  float shrink = 1.f;                       // SSD_LOCAL: the product of the chunk's decays
+  for (int c0 = t0; c0 < t1; c0 += kSsdPiece) {
+    const int nt = min(kSsdPiece, t1 - c0);
     __syncthreads();
     for (int idx = tid; idx < nt * N; idx += blockDim.x) {
       const int tk = idx / N, n = idx - tk * N;
-      const T* row = xbc + (size_t)(c0 + tk) * p.ld_xbc + inner + g * N;
-      Bs[idx] = to_f32(row[n]);
-      Cs[idx] = to_f32(row[p.G * N + n]);
+      const T* rowp = xbc + (size_t)(c0 + tk) * p.ld_xbc + inner + g * N;
+      Bs[idx] = to_f32(rowp[n]);
+      if (MODE != SSD_LOCAL) Cs[idx] = to_f32(rowp[p.G * N + n]);
     }
     for (int idx = tid; idx < nt * my_cols; idx += blockDim.x) {
       const int tk = idx / my_cols, q = idx - tk * my_cols;
@@ -268,6 +358,15 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
       const float xv = xs[tk * cols + pc];
       const float w = dts[tk] * xv, da = das[tk];
       const float* Bt = Bs + tk * N;
+      if (MODE == SSD_LOCAL) {
+        shrink *= da;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+          const int n = l + 4 * i;
+          if (n < N) S[i] = fmaf(da, S[i], w * Bt[n]);
+        }
+        continue;
+      }
       const float* Ct = Cs + tk * N;
       float acc = 0.f;
 #pragma unroll
@@ -283,44 +382,85 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
       if (owner && l == 0) p.y[(size_t)(c0 + tk) * inner + h * p.Dv + col0 + pc] = fmaf(dskip, xv, acc);
     }
   }
-  if (owner) {
+  if (owner && to) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
       const int n = l + 4 * i;
-      if (n < N) st[n] = S[i];
+      if (n < N) to[n] = S[i];
     }
+  }
+  if (MODE == SSD_LOCAL && tid == 0 && col0 == 0) p.decay[row * p.H + h] = shrink;
+}
+
+// One thread per element of a request's matrices walks the run's chunks in order and replaces, in `carry`, what a
+// chunk ends with from zero by what it begins with.  Runs of one chunk are left alone.
+__global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs p) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const size_t per = (size_t)p.H * p.Dv * p.N;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per) return;
+  const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
+  if (t0 + p.chunk >= t1) return;
+  const int h = (int)(e / ((size_t)p.Dv * p.N));
+  float S = p.req_start[r] > 0 ? p.state[(size_t)p.slots[r] * p.slot_stride + e] : 0.f;
+  for (int t = t0; t < t1; t += p.chunk) {
+    const size_t row = (size_t)(r - p.row_off) + t / p.chunk;
+    float* m = p.carry + row * per + e;
+    if (t + p.chunk >= t1) { *m = S; break; }
+    const float local = *m;
+    *m = S;
+    S = fmaf(p.decay[row * p.H + h], S, local);
   }
 }
 
-// cols: value columns per block (the launcher of a lone long run spreads a head over several blocks).
-KVB_EXPORT int kvb_ssd_scan(const SsdArgs* args, int R, int dtype, cudaStream_t stream) {
+// Without chunks: cols, the value columns per block, shrink until the grid has about as many blocks as there are SMs.
+// max_run: the step's longest run (chunked launches only: the grid's third extent).
+KVB_EXPORT int kvb_ssd_scan(const SsdArgs* args, int R, int max_run, int dtype, cudaStream_t stream) {
   SsdArgs p = *args;
   if (R <= 0) return 0;
   if (p.H < 1 || p.G < 1 || p.H % p.G || p.N < 1 || p.N > 256 || p.Dv < 1 || R > 65535) return KVB_ERR_BAD_SIZE;
-  // as many columns per block as keep the grid at about the number of SMs, at most 256 threads' worth
   int cols = p.Dv < 64 ? p.Dv : 64;
-  while (cols > 8 && (long long)p.H * ((p.Dv + cols - 1) / cols) * R < kvb_sm_count()) cols = (cols + 1) / 2;
+  unsigned nck = 1;
+  if (p.chunk > 0) {
+    if (!p.carry || !p.decay || max_run < 1 || p.chunk % kSsdPiece) return KVB_ERR_BAD_SIZE;
+    nck = (unsigned)((max_run + p.chunk - 1) / p.chunk);
+    if (nck > 65535) return KVB_ERR_BAD_SIZE;
+  }
+  while (cols > 8 && (long long)p.H * ((p.Dv + cols - 1) / cols) * R * nck < kvb_sm_count()) cols = (cols + 1) / 2;
   p.cols = cols;
   const int splits = (p.Dv + cols - 1) / cols;
   const int threads = (cols * 4 + 31) / 32 * 32;
-  const size_t smem = ((size_t)kSsdChunk * (2 * p.N + cols) + 2 * kSsdChunk) * sizeof(float);
+  const size_t smem = ((size_t)kSsdPiece * (2 * p.N + cols) + 2 * kSsdPiece) * sizeof(float);
   const int npt = (p.N + 3) / 4;
-#define KVB_SSD(NPT)                                                                                              \
+  const dim3 grid(p.H * splits, R, nck);
+#define KVB_SSD_MODE(NPT, MODE)                                                                                    \
   {                                                                                                                \
     if (smem > 48 * 1024) {                                                                                        \
-      cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                           (int)smem);                                                             \
+      cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, MODE>,                                          \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    kvb_launch(ssd_scan_kernel<T, NPT>, dim3(p.H * splits, R), dim3(threads), smem, stream, p);                    \
+    kvb_launch(ssd_scan_kernel<T, NPT, MODE>, grid, dim3(threads), smem, stream, p);                               \
   }
-  KVB_DISPATCH_DTYPE(dtype, T, {
-    if (npt <= 8) KVB_SSD(8)
-    else if (npt <= 16) KVB_SSD(16)
-    else if (npt <= 32) KVB_SSD(32)
-    else KVB_SSD(64)
-  });
+#define KVB_SSD(MODE)                                                                                              \
+  KVB_DISPATCH_DTYPE(dtype, T, {                                                                                   \
+    if (npt <= 8) KVB_SSD_MODE(8, MODE)                                                                            \
+    else if (npt <= 16) KVB_SSD_MODE(16, MODE)                                                                     \
+    else if (npt <= 32) KVB_SSD_MODE(32, MODE)                                                                     \
+    else KVB_SSD_MODE(64, MODE)                                                                                    \
+  })
+  if (p.chunk > 0) {
+    KVB_SSD(SSD_LOCAL);
+    const size_t per = (size_t)p.H * p.Dv * p.N;
+    kvb_launch(ssd_carry_kernel, dim3((unsigned)((per + 255) / 256), R), dim3(256), 0, stream, p);
+    KVB_SSD(SSD_FINAL);
+  } else {
+    KVB_SSD(SSD_WHOLE);
+  }
 #undef KVB_SSD
+#undef KVB_SSD_MODE
   return kvb_launch_result();
 }
 

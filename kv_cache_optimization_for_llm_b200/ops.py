@@ -1011,10 +1011,29 @@ def _bmm_f32_ok() -> bool:
     return _bmm_f32
 
 
+# Runs of at least this many tokens are cut into chunks that the scans below walk side by side (the states that
+# the chunks begin with then come from per-chunk summaries, which rounds differently from one walk).
+SCAN_CHUNK_MIN_RUN = int(os.environ.get('KVB200_SCAN_CHUNK_MIN_RUN', '256'))
+
+
+def _chunk_rows(batch, chunk: int):
+    """For a step whose runs are cut into chunks of ``chunk`` tokens: (rows of per-chunk scratch, first request row
+    that may have more than one chunk).  Request row r's chunk that begins at token row t uses scratch row
+    ``r - first + t // chunk``."""
+    first = 0
+    qs = batch.host.get("q_start") if getattr(batch, "host", None) else None
+    if qs is not None:
+        runs = qs[1:batch.num_reqs + 1] - qs[:batch.num_reqs]
+        long_runs = (runs > chunk).nonzero()[0]
+        first = int(long_runs[0]) if len(long_runs) else batch.num_reqs
+    return batch.num_reqs - first + batch.num_tokens // chunk + 1, first
+
+
 class _DiagArgs(ctypes.Structure):
     _fields_ = [("a", c_void_p), ("b", c_void_p), ("y", c_void_p), ("ld_y", c_int), ("y_bias", c_void_p),
                 ("out_scale", c_float), ("out", c_void_p), ("state", c_void_p), ("slot_stride", c_longlong),
-                ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("C", c_int)]
+                ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("C", c_int),
+                ("chunked", c_int), ("row_off", c_int), ("sum_a", c_void_p), ("sum_b", c_void_p), ("begin", c_void_p)]
 
 
 def diag_scan(a: torch.Tensor, b: torch.Tensor, y, y_bias: Optional[torch.Tensor], out_scale: float,
@@ -1022,17 +1041,28 @@ def diag_scan(a: torch.Tensor, b: torch.Tensor, y, y_bias: Optional[torch.Tensor
     """``S_t = a_t S_{t-1} + b_t`` per channel along every request's tokens of the step, from the state in the
     request's slot (zero for a request that starts at position 0), which is left up to date.  ``y``: (tensor,
     first column) of the gate branch [T, C] before its activation.  Returns
-    ``S_t * gelu_tanh(y_t + y_bias) * out_scale`` [T, C]."""
+    ``S_t * gelu_tanh(y_t + y_bias) * out_scale`` [T, C].  A step with a run of ``SCAN_CHUNK_MIN_RUN`` tokens or
+    more walks chunks of its runs side by side."""
     _need_cuda(a, b, state)
     T, C = a.shape
     yt, ycol = y
     assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
     assert yt.dtype == out_dtype and yt.stride(1) == 1 and state.dtype == torch.float32 and state.stride(1) == 1
     out = new((T, C), out_dtype, a.device)
+    max_run = int(getattr(batch, "max_q_len", 0) or 0)
+    chunked = max_run >= SCAN_CHUNK_MIN_RUN and not _capturing()
+    sa = sb = begin = first = 0
+    if chunked:
+        rows, first = _chunk_rows(batch, lib("recurrence").kvb_diag_chunk())
+        pairs = new((2, rows, C), torch.float32, a.device)
+        begin_t = new((batch.num_reqs, C), torch.float32, a.device)
+        sa, sb, begin = pairs[0].data_ptr(), pairs[1].data_ptr(), begin_t.data_ptr()
+        choices["diag_scan_chunked"] += 1
     p = _DiagArgs(a.data_ptr(), b.data_ptr(), _at(yt, ycol), yt.stride(0), 0 if y_bias is None else y_bias.data_ptr(),
                   float(out_scale), out.data_ptr(), state.data_ptr(), state.stride(0), batch.q_start.data_ptr(),
-                  batch.req_start.data_ptr(), batch.slots.data_ptr(), C)
-    rc = lib("recurrence").kvb_diag_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(dtype_code(out_dtype)), _stream())
+                  batch.req_start.data_ptr(), batch.slots.data_ptr(), C, int(chunked), first, sa, sb, begin)
+    rc = lib("recurrence").kvb_diag_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(max_run),
+                                         c_int(dtype_code(out_dtype)), _stream())
     _check(rc, "diag_scan")
     return out
 
@@ -1041,7 +1071,8 @@ class _SsdArgs(ctypes.Structure):
     _fields_ = [("xbc", c_void_p), ("ld_xbc", c_int), ("dt", c_void_p), ("ld_dt", c_int), ("dt_bias", c_void_p),
                 ("A_log", c_void_p), ("D", c_void_p), ("state", c_void_p), ("slot_stride", c_longlong), ("y", c_void_p),
                 ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int),
-                ("N", c_int), ("Dv", c_int), ("cols", c_int)]
+                ("N", c_int), ("Dv", c_int), ("cols", c_int), ("chunk", c_int), ("row_off", c_int),
+                ("carry", c_void_p), ("decay", c_void_p)]
 
 
 def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
@@ -1050,7 +1081,8 @@ def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, 
     step:  ``dt = softplus(dt_raw + dt_bias)``, ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D x``.
     ``xbc`` [T, heads dv + 2 groups n]: x | B | C (head h reads group ``h // (heads / groups)``); ``dt``: (tensor, first
     column) of the raw step sizes [T, heads].  ``state``: float32 [slots, >= heads * dv * n], zero for a request
-    that starts at position 0.  Returns float32 y [T, heads * dv]."""
+    that starts at position 0.  Returns float32 y [T, heads * dv].  A step with a run of ``SCAN_CHUNK_MIN_RUN``
+    tokens or more walks chunks of its runs side by side (64 tokens a chunk, 128 from runs of 1024 on)."""
     _need_cuda(xbc, state)
     T = xbc.shape[0]
     dtt, dcol = dt
@@ -1059,10 +1091,20 @@ def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, 
     for v in (dt_bias, a_log, d_skip):
         assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
     y = new((T, heads * dv), torch.float32, xbc.device)
+    max_run = int(getattr(batch, "max_q_len", 0) or 0)
+    chunk = first = carry = decay = 0
+    if max_run >= SCAN_CHUNK_MIN_RUN and not _capturing():
+        chunk = 128 if max_run >= 1024 else 64
+        rows, first = _chunk_rows(batch, chunk)
+        carry_t = new((rows, heads * dv * n), torch.float32, xbc.device)
+        decay_t = new((rows, heads), torch.float32, xbc.device)
+        carry, decay = carry_t.data_ptr(), decay_t.data_ptr()
+        choices["ssd_scan_chunked"] += 1
     p = _SsdArgs(xbc.data_ptr(), xbc.stride(0), _at(dtt, dcol), dtt.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
                  d_skip.data_ptr(), state.data_ptr(), state.stride(0), y.data_ptr(), batch.q_start.data_ptr(),
-                 batch.req_start.data_ptr(), batch.slots.data_ptr(), heads, groups, n, dv, 0)
-    rc = lib("recurrence").kvb_ssd_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(dtype_code(xbc.dtype)), _stream())
+                 batch.req_start.data_ptr(), batch.slots.data_ptr(), heads, groups, n, dv, 0, chunk, first, carry, decay)
+    rc = lib("recurrence").kvb_ssd_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(max_run),
+                                        c_int(dtype_code(xbc.dtype)), _stream())
     _check(rc, "ssd_scan")
     return y
 
