@@ -262,8 +262,9 @@ KVB_EXPORT int kvb_diag_scan(const DiagArgs* args, int R, int max_run, int dtype
 
 // ---------------------------------------------------------------- matrix state with a decay per head
 // A block owns `cols` value columns of one (request, head); four lanes share a column, lane l holding state rows
-// l, l + 4, ... (NPT of them) in registers for the whole run.  The run is walked in pieces of 16 tokens whose B, C,
-// x and step sizes the block first brings into shared memory as float32.
+// l, l + 4, ... (NPT of them) in registers for the whole run; where N is a multiple of 4 (VEC) the lane holds rows
+// 16 j + 4 l .. + 3 instead, so that one shared-memory load brings four rows of B or C.  The run is walked in pieces
+// of 32 tokens whose B, C, x and step sizes the block first brings into shared memory as float32.
 //
 // A long run is cut into chunks of `chunk` tokens that are walked side by side, in three launches:
 //   SSD_LOCAL   every chunk but a run's last, from a zero state: the state it ends with and the product of its decays
@@ -283,12 +284,12 @@ struct SsdArgs {
   float* carry; float* decay;            // chunked: [rows][H][Dv][N] and [rows][H]
 };
 
-constexpr int kSsdPiece = 16;
+constexpr int kSsdPiece = 32;
 enum { SSD_WHOLE = 0, SSD_LOCAL = 1, SSD_FINAL = 2 };
 
-template <typename T, int NPT, int MODE>
+template <typename T, int NPT, int MODE, bool VEC>
 __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
-  extern __shared__ float ssm[];
+  extern __shared__ __align__(16) float ssm[];
   const int N = p.N, cols = p.cols;
   float* Bs = ssm;                          // [piece][N]
   float* Cs = Bs + kSsdPiece * N;           // [piece][N]
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
   float S[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
-    const int n = l + 4 * i;
+    const int n = VEC ? 16 * (i >> 2) + 4 * l + (i & 3) : l + 4 * i;
     S[i] = (from && owner && n < N) ? from[n] : 0.f;
   }
   const T* xbc = static_cast<const T*>(p.xbc);
@@ -360,21 +361,56 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
       const float* Bt = Bs + tk * N;
       if (MODE == SSD_LOCAL) {
         shrink *= da;
+        if (VEC) {
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
-          const int n = l + 4 * i;
-          if (n < N) S[i] = fmaf(da, S[i], w * Bt[n]);
+          for (int j = 0; j < NPT / 4; ++j) {
+            const int n = 16 * j + 4 * l;
+            if (n < N) {
+              const float4 bv = *reinterpret_cast<const float4*>(Bt + n);
+              S[4 * j + 0] = fmaf(da, S[4 * j + 0], w * bv.x);
+              S[4 * j + 1] = fmaf(da, S[4 * j + 1], w * bv.y);
+              S[4 * j + 2] = fmaf(da, S[4 * j + 2], w * bv.z);
+              S[4 * j + 3] = fmaf(da, S[4 * j + 3], w * bv.w);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) {
+            const int n = l + 4 * i;
+            if (n < N) S[i] = fmaf(da, S[i], w * Bt[n]);
+          }
         }
         continue;
       }
       const float* Ct = Cs + tk * N;
       float acc = 0.f;
+      if (VEC) {
+        float a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const int n = l + 4 * i;
-        if (n < N) {
-          S[i] = fmaf(da, S[i], w * Bt[n]);
-          acc = fmaf(S[i], Ct[n], acc);
+        for (int j = 0; j < NPT / 4; ++j) {
+          const int n = 16 * j + 4 * l;
+          if (n < N) {
+            const float4 bv = *reinterpret_cast<const float4*>(Bt + n);
+            const float4 cv = *reinterpret_cast<const float4*>(Ct + n);
+            S[4 * j + 0] = fmaf(da, S[4 * j + 0], w * bv.x);
+            S[4 * j + 1] = fmaf(da, S[4 * j + 1], w * bv.y);
+            S[4 * j + 2] = fmaf(da, S[4 * j + 2], w * bv.z);
+            S[4 * j + 3] = fmaf(da, S[4 * j + 3], w * bv.w);
+            acc = fmaf(S[4 * j + 0], cv.x, acc);
+            a1 = fmaf(S[4 * j + 1], cv.y, a1);
+            a2 = fmaf(S[4 * j + 2], cv.z, a2);
+            a3 = fmaf(S[4 * j + 3], cv.w, a3);
+          }
+        }
+        acc = (acc + a1) + (a2 + a3);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+          const int n = l + 4 * i;
+          if (n < N) {
+            S[i] = fmaf(da, S[i], w * Bt[n]);
+            acc = fmaf(S[i], Ct[n], acc);
+          }
         }
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -385,7 +421,7 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
   if (owner && to) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-      const int n = l + 4 * i;
+      const int n = VEC ? 16 * (i >> 2) + 4 * l + (i & 3) : l + 4 * i;
       if (n < N) to[n] = S[i];
     }
   }
@@ -435,22 +471,26 @@ KVB_EXPORT int kvb_ssd_scan(const SsdArgs* args, int R, int max_run, int dtype, 
   const size_t smem = ((size_t)kSsdPiece * (2 * p.N + cols) + 2 * kSsdPiece) * sizeof(float);
   const int npt = (p.N + 3) / 4;
   const dim3 grid(p.H * splits, R, nck);
-#define KVB_SSD_MODE(NPT, MODE)                                                                                    \
+#define KVB_SSD_MODE(NPT, MODE, VEC)                                                                                  \
   {                                                                                                                \
     if (smem > 48 * 1024) {                                                                                        \
-      cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, MODE>,                                          \
+      cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, MODE, VEC>,                                     \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    kvb_launch(ssd_scan_kernel<T, NPT, MODE>, grid, dim3(threads), smem, stream, p);                               \
+    kvb_launch(ssd_scan_kernel<T, NPT, MODE, VEC>, grid, dim3(threads), smem, stream, p);                          \
   }
-#define KVB_SSD(MODE)                                                                                              \
+#define KVB_SSD_VEC(MODE, VEC)                                                                                     \
   KVB_DISPATCH_DTYPE(dtype, T, {                                                                                   \
-    if (npt <= 8) KVB_SSD_MODE(8, MODE)                                                                            \
-    else if (npt <= 16) KVB_SSD_MODE(16, MODE)                                                                     \
-    else if (npt <= 32) KVB_SSD_MODE(32, MODE)                                                                     \
-    else KVB_SSD_MODE(64, MODE)                                                                                    \
+    if (npt <= 8) KVB_SSD_MODE(8, MODE, VEC)                                                                       \
+    else if (npt <= 16) KVB_SSD_MODE(16, MODE, VEC)                                                                \
+    else if (npt <= 32) KVB_SSD_MODE(32, MODE, VEC)                                                                \
+    else KVB_SSD_MODE(64, MODE, VEC)                                                                               \
   })
+#define KVB_SSD(MODE)                                                                                              \
+  {                                                                                                                \
+    if (p.N % 4 == 0) KVB_SSD_VEC(MODE, true) else KVB_SSD_VEC(MODE, false)                                        \
+  }
   if (p.chunk > 0) {
     KVB_SSD(SSD_LOCAL);
     const size_t per = (size_t)p.H * p.Dv * p.N;
@@ -460,6 +500,7 @@ KVB_EXPORT int kvb_ssd_scan(const SsdArgs* args, int R, int max_run, int dtype, 
     KVB_SSD(SSD_WHOLE);
   }
 #undef KVB_SSD
+#undef KVB_SSD_VEC
 #undef KVB_SSD_MODE
   return kvb_launch_result();
 }
