@@ -270,7 +270,9 @@ KVB_EXPORT int kvb_diag_scan(const DiagArgs* args, int R, int max_run, int dtype
 //   SSD_LOCAL   every chunk but a run's last, from a zero state: the state it ends with and the product of its decays
 //   ssd_carry   per state element, along the run's chunks in order: what each chunk begins with (S <- decay S + local)
 //   SSD_FINAL   every chunk from what it begins with, writing y; the run's last chunk leaves the state in the slot
-// Request row r's chunk that begins at token row t keeps its matrices in row (r - row_off) + t / chunk of `carry`.
+// Request row r's chunk that begins at token row t keeps its matrices in row (r - row_off) + t / chunk of `local`
+// (what it ends with from zero) and of `carry` (what it begins with): two arrays, so that the middle launch's loads
+// do not wait for its stores.
 // A run of one chunk reads and writes its slot directly.
 struct SsdArgs {
   const void* xbc; int ld_xbc;           // [T, >= inner + 2 G N] compute type: x | B | C behind the convolution
@@ -281,7 +283,7 @@ struct SsdArgs {
   const int* q_start; const int* req_start; const int* slots;
   int H, G, N, Dv, cols;
   int chunk, row_off;                    // chunk > 0: runs are cut; requests below row_off are single chunks
-  float* carry; float* decay;            // chunked: [rows][H][Dv][N] and [rows][H]
+  float* local; float* carry; float* decay;   // chunked: [rows][H][Dv][N] twice and [rows][H]
 };
 
 constexpr int kSsdPiece = 32;
@@ -320,9 +322,9 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
     const bool single = t0 + p.chunk >= t1;                      // a run of one chunk
     if (MODE == SSD_LOCAL ? mine + p.chunk >= t1 : (mine >= t1 && blockIdx.z > 0)) return;
     row = (size_t)(r - p.row_off) + mine / p.chunk;
-    float* mat = p.carry + row * (size_t)inner * N + at;
-    if (MODE == SSD_LOCAL) { from = nullptr; to = mat; }
-    else if (!single) { from = mat; to = mine + p.chunk >= t1 ? st : nullptr; }
+    const size_t mat = row * (size_t)inner * N + at;
+    if (MODE == SSD_LOCAL) { from = nullptr; to = p.local + mat; }
+    else if (!single) { from = p.carry + mat; to = mine + p.chunk >= t1 ? st : nullptr; }
     t0 = mine;
     t1 = min(t1, mine + p.chunk);
   }
@@ -428,8 +430,8 @@ __global__ void __launch_bounds__(256) ssd_scan_kernel(SsdArgs p) {
   if (MODE == SSD_LOCAL && tid == 0 && col0 == 0) p.decay[row * p.H + h] = shrink;
 }
 
-// One thread per element of a request's matrices walks the run's chunks in order and replaces, in `carry`, what a
-// chunk ends with from zero by what it begins with.  Runs of one chunk are left alone.
+// One thread per element of a request's matrices walks the run's chunks in order and writes what each begins with.
+// Runs of one chunk are left alone.  The loads (four chunks' at a time) depend on no store.
 __global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs p) {
   pdl_trigger();
   pdl_wait();
@@ -439,15 +441,30 @@ __global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs p) {
   if (e >= per) return;
   const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
   if (t0 + p.chunk >= t1) return;
-  const int h = (int)(e / ((size_t)p.Dv * p.N));
+  const int h = (int)((unsigned)e / ((unsigned)p.Dv * (unsigned)p.N));
+  const float* __restrict__ local = p.local;
+  const float* __restrict__ decay = p.decay;
+  float* __restrict__ carry = p.carry;
   float S = p.req_start[r] > 0 ? p.state[(size_t)p.slots[r] * p.slot_stride + e] : 0.f;
-  for (int t = t0; t < t1; t += p.chunk) {
-    const size_t row = (size_t)(r - p.row_off) + t / p.chunk;
-    float* m = p.carry + row * per + e;
-    if (t + p.chunk >= t1) { *m = S; break; }
-    const float local = *m;
-    *m = S;
-    S = fmaf(p.decay[row * p.H + h], S, local);
+  const int nck = (t1 - t0 + p.chunk - 1) / p.chunk;
+  const size_t row0 = (size_t)(r - p.row_off) + t0 / p.chunk;      // rows of one run follow one another
+  int k = 0;
+  for (; k + 4 < nck; k += 4) {
+    float lo[4], de[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      lo[x] = local[(row0 + k + x) * per + e];
+      de[x] = decay[(row0 + k + x) * p.H + h];
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      carry[(row0 + k + x) * per + e] = S;
+      S = fmaf(de[x], S, lo[x]);
+    }
+  }
+  for (; k < nck; ++k) {
+    carry[(row0 + k) * per + e] = S;
+    if (k + 1 < nck) S = fmaf(decay[(row0 + k) * p.H + h], S, local[(row0 + k) * per + e]);
   }
 }
 
@@ -460,7 +477,8 @@ KVB_EXPORT int kvb_ssd_scan(const SsdArgs* args, int R, int max_run, int dtype, 
   int cols = p.Dv < 64 ? p.Dv : 64;
   unsigned nck = 1;
   if (p.chunk > 0) {
-    if (!p.carry || !p.decay || max_run < 1 || p.chunk % kSsdPiece) return KVB_ERR_BAD_SIZE;
+    if (!p.local || !p.carry || !p.decay || max_run < 1 || p.chunk % kSsdPiece) return KVB_ERR_BAD_SIZE;
+    if ((long long)p.H * p.Dv * p.N > 0x7fffffffLL) return KVB_ERR_BAD_SIZE;
     nck = (unsigned)((max_run + p.chunk - 1) / p.chunk);
     if (nck > 65535) return KVB_ERR_BAD_SIZE;
   }

@@ -1072,7 +1072,7 @@ class _SsdArgs(ctypes.Structure):
                 ("A_log", c_void_p), ("D", c_void_p), ("state", c_void_p), ("slot_stride", c_longlong), ("y", c_void_p),
                 ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int),
                 ("N", c_int), ("Dv", c_int), ("cols", c_int), ("chunk", c_int), ("row_off", c_int),
-                ("carry", c_void_p), ("decay", c_void_p)]
+                ("local", c_void_p), ("carry", c_void_p), ("decay", c_void_p)]
 
 
 def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
@@ -1092,17 +1092,17 @@ def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, 
         assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
     y = new((T, heads * dv), torch.float32, xbc.device)
     max_run = int(getattr(batch, "max_q_len", 0) or 0)
-    chunk = first = carry = decay = 0
+    chunk = first = local = carry = decay = 0
     if max_run >= SCAN_CHUNK_MIN_RUN and not _capturing():
         chunk = 128 if max_run >= 1024 else 64
         rows, first = _chunk_rows(batch, chunk)
-        carry_t = new((rows, heads * dv * n), torch.float32, xbc.device)
+        mats = new((2, rows, heads * dv * n), torch.float32, xbc.device)
         decay_t = new((rows, heads), torch.float32, xbc.device)
-        carry, decay = carry_t.data_ptr(), decay_t.data_ptr()
+        local, carry, decay = mats[0].data_ptr(), mats[1].data_ptr(), decay_t.data_ptr()
         choices["ssd_scan_chunked"] += 1
     p = _SsdArgs(xbc.data_ptr(), xbc.stride(0), _at(dtt, dcol), dtt.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
                  d_skip.data_ptr(), state.data_ptr(), state.stride(0), y.data_ptr(), batch.q_start.data_ptr(),
-                 batch.req_start.data_ptr(), batch.slots.data_ptr(), heads, groups, n, dv, 0, chunk, first, carry, decay)
+                 batch.req_start.data_ptr(), batch.slots.data_ptr(), heads, groups, n, dv, 0, chunk, first, local, carry, decay)
     rc = lib("recurrence").kvb_ssd_scan(ctypes.byref(p), c_int(batch.num_reqs), c_int(max_run),
                                         c_int(dtype_code(xbc.dtype)), _stream())
     _check(rc, "ssd_scan")
