@@ -461,3 +461,115 @@ class NonetarConfig:
         if cfg.vocab < 1 or cfg.width < 1 or not cfg.norm_eps > 0 or cfg.streams < 1:
             raise ConfigError("config.json: vocab, width and streams must be positive and norm.eps above zero")
         return cfg
+
+
+@dataclass(frozen=True)
+class TevanexLayerConfig:
+    """One entry of ``layers``: the mixer's kind (``mlstm``, ``attention`` or ``attention_2``) and sizes, the
+    feed-forward (None: the layer has only its mixer), and ``weights_of``: the layer whose tensors this one uses
+    (None: its own)."""
+    type: str
+    mixer: Mapping[str, Any]
+    mlp: Optional[Mapping[str, Any]]
+    weights_of: Optional[int] = None
+
+
+_TEVANEX_MIXER_KEYS = {
+    "mlstm": ("heads", "dim", "vdim", "gate_cap"),
+    "attention": ("heads", "kv_heads", "dim", "vdim", "scale"),
+    "attention_2": ("heads", "kv_heads", "dim", "vdim", "scale"),
+}
+
+
+@dataclass(frozen=True)
+class TevanexConfig:
+    """The keys of a Tevanex config.json: ``vocab``, ``width``, ``norm.eps``, ``embedding.scale``, ``residual_mult``,
+    ``logit_scale``, ``logit_softcap`` and ``layers`` (each with ``type``, ``mixer``, ``mlp`` and optionally
+    ``weights_of``).  An ``mlstm`` mixer names ``heads``, ``dim``, ``vdim``, ``gate_cap``; the two attentions ``heads``,
+    ``kv_heads``, ``dim``, ``vdim``, ``scale`` and optionally ``mask.size``, ``rot`` (``base``, ``dims``, and for the
+    second kind ``scaling`` with ``factor``, ``original``, ``fast``, ``slow``) and ``softcap``.  A feed-forward is of
+    ``kind`` ``moe``: ``expert`` (``ff``, ``limit``), ``router`` (``experts``, ``top``) and optionally ``shared``
+    (``ff``, ``limit``)."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    embedding_scale: float
+    residual_mult: float
+    logit_scale: float
+    logit_softcap: float
+    layers: Tuple[TevanexLayerConfig, ...]
+    max_position_embeddings: int
+    eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "TevanexConfig":
+        norm = d.get("norm") or {}
+        entries = list(d.get("layers") or [])
+        layers = []
+        for i, entry in enumerate(entries):
+            kind = entry.get("type")
+            if kind not in _TEVANEX_MIXER_KEYS:
+                raise ConfigError(f"config.json: layer {i} has a mixer of type {kind!r}; known: "
+                                  + ", ".join(sorted(_TEVANEX_MIXER_KEYS)))
+            mixer = entry.get("mixer") or {}
+            for key in _TEVANEX_MIXER_KEYS[kind]:
+                if mixer.get(key) is None:
+                    raise ConfigError(f"config.json: layer {i} ({kind}): mixer key {key!r} is missing")
+            if kind != "mlstm":
+                if int(mixer["kv_heads"]) < 1 or int(mixer["heads"]) % int(mixer["kv_heads"]):
+                    raise ConfigError(f"config.json: layer {i}: {mixer['heads']} query heads cannot be grouped over "
+                                      f"{mixer['kv_heads']} key/value heads")
+                rot = mixer.get("rot")
+                if rot:
+                    for key in ("base", "dims"):
+                        if rot.get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mixer.rot.{key} is missing")
+                    if int(rot["dims"]) % 2 or int(rot["dims"]) > int(mixer["dim"]):
+                        raise ConfigError(f"config.json: layer {i}: mixer.rot.dims must be even and at most mixer.dim")
+                    for key in ("factor", "original", "fast", "slow") if rot.get("scaling") else ():
+                        if rot["scaling"].get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mixer.rot.scaling.{key} is missing")
+                if mixer.get("mask") and int(mixer["mask"].get("size") or 0) < 1:
+                    raise ConfigError(f"config.json: layer {i}: mixer.mask.size must be a positive number of positions")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "moe":
+                    raise ConfigError(f"config.json: layer {i}: a feed-forward of kind {mlp.get('kind')!r} is not known "
+                                      "(known: 'moe')")
+                for group, keys in (("expert", ("ff", "limit")), ("router", ("experts", "top"))):
+                    for key in keys:
+                        if (mlp.get(group) or {}).get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mlp.{group}.{key} is missing")
+                if mlp.get("shared"):
+                    for key in ("ff", "limit"):
+                        if mlp["shared"].get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mlp.shared.{key} is missing")
+                if not 1 <= int(mlp["router"]["top"]) <= int(mlp["router"]["experts"]):
+                    raise ConfigError(f"config.json: layer {i}: mlp.router.top must lie between 1 and mlp.router.experts")
+            src = entry.get("weights_of")
+            if src is not None:
+                src = int(src)
+                if not 0 <= src < len(entries) or src == i or entries[src].get("weights_of") is not None:
+                    raise ConfigError(f"config.json: layer {i}: weights_of {src} must name another layer that has "
+                                      "tensors of its own")
+                if entries[src].get("type") != kind:
+                    raise ConfigError(f"config.json: layer {i} is of type {kind!r} but uses the tensors of layer {src}, "
+                                      f"which is of type {entries[src].get('type')!r}")
+            layers.append(TevanexLayerConfig(str(kind), dict(mixer), dict(mlp) if mlp is not None else None, src))
+        if not layers:
+            raise ConfigError("config.json: 'layers' is missing or empty")
+        eos = d.get("eos_token_id")
+        eos_ids = () if eos is None else (tuple(int(e) for e in eos) if isinstance(eos, (list, tuple)) else (int(eos),))
+        emb = d.get("embedding") or {}
+        cfg = cls(architecture=str(d.get("architecture") or (d.get("architectures") or ["Tevanex"])[0]),
+                  vocab=_need(d, "vocab", int), width=_need(d, "width", int), norm_eps=_need(norm, "eps", float),
+                  embedding_scale=float(emb["scale"]) if emb.get("scale") is not None else 1.0,
+                  residual_mult=float(d["residual_mult"]) if d.get("residual_mult") is not None else 1.0,
+                  logit_scale=float(d["logit_scale"]) if d.get("logit_scale") is not None else 1.0,
+                  logit_softcap=float(d["logit_softcap"]) if d.get("logit_softcap") else 0.0,
+                  layers=tuple(layers), max_position_embeddings=int(d.get("max_position_embeddings") or 131072),
+                  eos_token_ids=eos_ids)
+        if cfg.vocab < 1 or cfg.width < 1 or not cfg.norm_eps > 0:
+            raise ConfigError("config.json: vocab and width must be positive and norm.eps above zero")
+        return cfg

@@ -5,14 +5,15 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// residual[t, :] = table[ids[t], :]   (upstream: base/src/kernels.cu:279-287)
+// residual[t, :] = table[ids[t], :] * scale, the factor applied in float32   (upstream, without a factor:
+// base/src/kernels.cu:279-287)
 // An id below zero names a token that the sampling kernel of the step before left on the
 // device: -(1 + r) stands for sampled[r] (n_sampled entries), so that a step can be
 // launched before the host has seen the tokens it starts from.
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     const int* __restrict__ sampled, int n_sampled,
-                                    float* __restrict__ resid, int H, int V, int* status) {
+                                    float* __restrict__ resid, int H, int V, float scale, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -24,15 +25,15 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* row = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) resid[(size_t)t * H + i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) resid[(size_t)t * H + i] = to_f32(row[i]) * scale;
 }
 
 KVB_EXPORT int kvb_embed_gather(const void* table, int dtype, const int* ids, const int* sampled, int n_sampled,
-                                float* resid, int T_, int H, int V, int* status, cudaStream_t stream) {
+                                float* resid, int T_, int H, int V, float scale, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(embed_gather_kernel<T>, dim3(T_), dim3(threads), 0, stream,
-                                            (const T*)table, ids, sampled, n_sampled, resid, H, V, status)));
+                                            (const T*)table, ids, sampled, n_sampled, resid, H, V, scale, status)));
   return kvb_launch_result();
 }
 

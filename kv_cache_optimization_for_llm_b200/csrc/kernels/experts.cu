@@ -1,14 +1,18 @@
 // A feed-forward made of many small experts of which every token uses a few.
 //
 //   * route_kernel: the router.  A block per up to eight tokens: logits z = W_r h in float32 (W_r float32, h as
-//     stored; or handed in by the caller, who made them with a product of float32 sums), scores s = softmax(z) over all experts, the `top` experts with the largest s + correction
-//     (ties go to the lower index), their weights s / (sum of the chosen s + 1e-20) * scale.  It
+//     stored; or handed in by the caller, who made them with a product of float32 sums), scores s = softmax(z) over
+//     all experts (or, score_fn 1, s = sigmoid(z) of each), the `top` experts with the largest s + correction
+//     (ties go to the lower index), their weights s / (sum of the chosen s + 1e-20) * scale (or, without renorm,
+//     s * scale).  It
 //     leaves a dense table gate[t, e] (0 for an expert that was not chosen) and, for the last
 //     `identity` experts, which have no matrices and hand their input on, the sum of their weights.
 //   * expert_act_kernel: the experts' first products lie side by side in one row, [E * F | shared];
 //     a[t, j] = relu(p[t, j])^2 * gate[t, j / F] for j < E * F, relu(p)^2 behind it (an expert that
 //     every token uses).  One product with the experts' stacked second matrices then adds up the chosen
 //     experts' outputs, weighted, in its float32 accumulator; what an unchosen expert adds is exactly 0.
+//   * limited_act_kernel: experts with a gate and an up product each, both limited, and the token's weight on the
+//     expert's input instead of its output (see there).
 //   * row_axpy_kernel: y[t] += c[t] * x[t], the identity experts' share.
 // Every sum is taken in an order that depends on the sizes only, so a token's result does not
 // depend on its neighbours in the step.
@@ -27,8 +31,9 @@ constexpr int kRouteTokens = 8;        // tokens a block routes at most: a route
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_router, const float* __restrict__ logits,
-             const float* __restrict__ correction, float* __restrict__ gate, float* __restrict__ identity_weight, int T_,
-             int K, int E, int n_identity, int top, float scale, int tb) {
+             int ld_logits, const float* __restrict__ correction, float* __restrict__ gate,
+             float* __restrict__ identity_weight, int T_, int K, int E, int n_identity, int top, float scale, int score_fn,
+             int renorm, int tb) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -41,7 +46,10 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
   float* part_all = c_all + (size_t)tb * n_all;         // [kRouteWarps][tb][n_all] the warps' sums (not with logits)
   float* x = part_all + (size_t)kRouteWarps * tb * n_all;   // [tb][K] the tokens' inputs, float32 (not with logits)
   if (logits != nullptr) {
-    for (int i = threadIdx.x; i < n_tok * n_all; i += blockDim.x) s_all[i] = logits[(size_t)t0 * n_all + i];
+    for (int i = threadIdx.x; i < n_tok * n_all; i += blockDim.x) {
+      const int tt = i / n_all, e = i - tt * n_all;
+      s_all[i] = logits[(size_t)(t0 + tt) * ld_logits + e];
+    }
   } else {
     for (int i = threadIdx.x; i < n_tok * K; i += blockDim.x) {
       const int tt = i / K, k = i - tt * K;
@@ -92,20 +100,25 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
     const int t = t0 + tt;
     float* s = s_all + (size_t)tt * n_all;
     float* c = c_all + (size_t)tt * n_all;
-    float zmax = -CUDART_INF_F;
-    for (int e = lane; e < n_all; e += 32) zmax = fmaxf(zmax, s[e]);
-    zmax = warp_max(zmax);
-    float sum = 0.f;
-    for (int e = lane; e < n_all; e += 32) {
-      const float v = expf(s[e] - zmax);
-      s[e] = v;
-      sum += v;
+    float sum = 1.f;
+    if (score_fn == 0) {
+      float zmax = -CUDART_INF_F;
+      for (int e = lane; e < n_all; e += 32) zmax = fmaxf(zmax, s[e]);
+      zmax = warp_max(zmax);
+      sum = 0.f;
+      for (int e = lane; e < n_all; e += 32) {
+        const float v = expf(s[e] - zmax);
+        s[e] = v;
+        sum += v;
+      }
+      sum = warp_sum(sum);
+    } else {
+      for (int e = lane; e < n_all; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
     }
-    sum = warp_sum(sum);
     __syncwarp();
     for (int e = lane; e < n_all; e += 32) {
       s[e] = s[e] / sum;
-      c[e] = s[e] + correction[e];
+      c[e] = s[e] + (correction != nullptr ? correction[e] : 0.f);
       gate[(size_t)t * n_all + e] = 0.f;
     }
     __syncwarp();
@@ -130,7 +143,7 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
       if (lane == 0) c[at] = -CUDART_INF_F;
       __syncwarp();
     }
-    const float norm = scale / (chosen_sum + 1e-20f);
+    const float norm = renorm ? scale / (chosen_sum + 1e-20f) : scale;
     float idw = 0.f;
     for (int r = 0; r < top; ++r) {
       const int e = __shfl_sync(0xffffffffu, mine, r);
@@ -143,12 +156,15 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
   }
 }
 
-// logits: float32 [T, E + n_identity], the router's products if the caller has made them (h and w_router are not
-// read then), else null.  Refuses: more than 32 chosen experts per token, more than 4096 experts, K above 16384.
-KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const float* logits, const float* correction,
-                         float* gate, float* identity_weight, int T_, int K, int E, int n_identity, int top, float scale,
-                         int dtype, cudaStream_t stream) {
+// logits: float32 [T, >= E + n_identity] with row stride ld_logits, the router's products if the caller has made them
+// (h and w_router are not read then), else null.  correction: may be null.  score_fn 0: softmax over all experts, 1: a
+// sigmoid of each.  renorm 0: the chosen scores are the weights as they are (times scale).
+// Refuses: more than 32 chosen experts per token, more than 4096 experts, K above 16384.
+KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const float* logits, int ld_logits,
+                         const float* correction, float* gate, float* identity_weight, int T_, int K, int E,
+                         int n_identity, int top, float scale, int score_fn, int renorm, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
+  if (score_fn < 0 || score_fn > 1 || (logits != nullptr && ld_logits < E + n_identity)) return KVB_ERR_BAD_SIZE;
   if (E < 0 || n_identity < 0 || E + n_identity < 1 || E + n_identity > 4096 || top < 1 || top > 32 || K < 1 || K > 16384)
     return KVB_ERR_BAD_SIZE;
   const int n_all = E + n_identity;
@@ -166,7 +182,7 @@ KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const f
       if (err != cudaSuccess) return (int)err;
     }
     kvb_launch(route_kernel<T>, dim3((T_ + tb - 1) / tb), dim3(kRouteWarps * 32), smem, stream, (const T*)h, ld_h, w_router,
-               logits, correction, gate, identity_weight, T_, K, E, n_identity, top, scale, tb);
+               logits, ld_logits, correction, gate, identity_weight, T_, K, E, n_identity, top, scale, score_fn, renorm, tb);
   });
   return kvb_launch_result();
 }
@@ -240,6 +256,60 @@ KVB_EXPORT int kvb_expert_act(const void* p, const float* gate, int ld_gate, voi
   const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(expert_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)p, gate,
                                             ld_gate, (T*)out, E * F, F, width, total)));
+  return kvb_launch_result();
+}
+
+// Experts of the form  down (a(g) (u + 1)),  g = min(w gate.h, limit),  u = clamp(w up.h, -limit, limit),
+// a(g) = g sigmoid(alpha g),  where w is the token's weight for the expert: it multiplies the expert's input, which for
+// matrices without biases is the same as multiplying both first products, before the limits.
+// p [T, ld_p]: per routed expert e its gate product (F features from column 2 e F) and its up product (the next F);
+// behind the E routed experts one that every token uses: S gate features, then S up features, with a limit of its own
+// and w = 1, whose result is multiplied by sigmoid(shared_logit[t * ld_s]) (float32; null: by 1), which for a last
+// matrix without bias is the same as multiplying its output.  gate [T, ld_gate] float32: the weights, 0 for an expert
+// that was not chosen.  out [T, E F + S + pad] dense, the padding columns zero.
+template <typename T>
+__global__ void limited_act_kernel(const T* __restrict__ p, int ld_p, const float* __restrict__ gate, int ld_gate,
+                                   const float* __restrict__ shared_logit, int ld_s, T* __restrict__ out, int E, int F,
+                                   int S, int width, float limit, float shared_limit, float alpha, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  const int EF = E * F;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width;
+    const int j = (int)(idx - t * width);
+    float a = 0.f;
+    if (j < EF) {
+      const int e = j / F, i = j - e * F;
+      const float w = gate[t * ld_gate + e];
+      if (w != 0.f) {
+        const float g = fminf(w * to_f32(p[t * ld_p + 2 * e * F + i]), limit);
+        const float u = fminf(fmaxf(w * to_f32(p[t * ld_p + 2 * e * F + F + i]), -limit), limit);
+        a = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+      }
+    } else if (j < EF + S) {
+      const int i = j - EF;
+      const float g = fminf(to_f32(p[t * ld_p + 2 * EF + i]), shared_limit);
+      const float u = fminf(fmaxf(to_f32(p[t * ld_p + 2 * EF + S + i]), -shared_limit), shared_limit);
+      a = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+      if (shared_logit != nullptr) a *= 1.0f / (1.0f + expf(-shared_logit[t * ld_s]));
+    }
+    out[idx] = from_f32<T>(a);
+  }
+}
+
+KVB_EXPORT int kvb_limited_act(const void* p, int ld_p, const float* gate, int ld_gate, const float* shared_logit,
+                               int ld_s, void* out, int T_, int E, int F, int S, int pad, float limit, float shared_limit,
+                               float alpha, int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  const int width = E * F + S + pad;
+  if (E < 0 || F < 1 || S < 0 || pad < 0 || E * F + S < 1 || ld_p < 2 * (E * F + S)) return KVB_ERR_BAD_SIZE;
+  const size_t total = (size_t)T_ * width;
+  const size_t want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(limited_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)p, ld_p,
+                                            gate, ld_gate, shared_logit, ld_s, (T*)out, E, F, S, width, limit,
+                                            shared_limit, alpha, total)));
   return kvb_launch_result();
 }
 

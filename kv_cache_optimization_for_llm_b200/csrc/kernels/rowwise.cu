@@ -45,7 +45,8 @@ __device__ __forceinline__ void row_stats(const float* row, int H, int kind, flo
 //   d = delta[t] + delta_bias                       (when a branch output is pending)
 //   v = resid[t] + post(d) * post_w                 post: layer norm, RMS norm or identity
 //   resid[t] = v                                    (only when every row is produced: rows == null)
-//   out[b] = pre(v) * pre_w                         pre: layer norm or RMS norm; NORM_NONE: no output
+//   out[b] = pre(v) * pre_w                         pre: layer norm or RMS norm; NORM_NONE: v itself in the
+//                                                   activations' type when out is given, else no output
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 add_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ delta_bias,
@@ -76,10 +77,15 @@ add_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const fl
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = resid[src + i];
   }
-  if (pre_kind == NORM_NONE) return;
+  T* o = out + (size_t)b * H;
+  if (pre_kind == NORM_NONE) {
+    // a sublayer that reads the stream itself: the thread that made an element hands it on
+    if (out != nullptr)
+      for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(row[i]);
+    return;
+  }
   __syncthreads();
   row_stats(row, H, pre_kind, pre_eps, part, mean, rstd);
-  T* o = out + (size_t)b * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x)
     o[i] = from_f32<T>((row[i] - mean) * rstd * (pre_w ? pre_w[i] : 1.f));
 }
@@ -177,6 +183,27 @@ KVB_EXPORT int kvb_bias_act_mul(const void* gu, const float* bias, void* out, in
   const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(bias_act_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gu,
                                             bias, (T*)out, I, kind, total)));
+  return kvb_launch_result();
+}
+
+// ---------------------------------------------------------------- logits: a factor, then a soft cap
+// x[i] <- cap * tanh(x[i] * scale / cap) in place on float32 (cap 0: only the factor).
+__global__ void scale_softcap_kernel(float* __restrict__ x, float scale, float cap, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const float z = x[idx] * scale;
+    x[idx] = cap > 0.f ? cap * tanhf(z / cap) : z;
+  }
+}
+
+KVB_EXPORT int kvb_scale_softcap(float* x, size_t total, float scale, float cap, cudaStream_t stream) {
+  if (total == 0) return 0;
+  if (cap < 0.f) return KVB_ERR_BAD_SIZE;
+  const size_t want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
+  kvb_launch(scale_softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, scale, cap, total);
   return kvb_launch_result();
 }
 

@@ -115,7 +115,7 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
   const int pos = positions[t];
   const int* table = block_table + (size_t)token_req[t] * max_pages;
   const int row_len = Dk + Dv;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;      // first key of the window
+  const int lo = first_seen_key(pos, window, shape.chunk);       // first key of the window or of the position's block
   const int keep = window > 0 ? keep_first : 0;                  // keys below it are seen whatever the window
   const int keep_chunks = (keep + 31) / 32;
   const int lo_chunk = lo / 32;
@@ -180,18 +180,23 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
   }
   __syncthreads();
   if (warp == 0) {
-    float M = one_more ? 0.f : -CUDART_INF_F;       // the one more key's score is 0
+    // what joins the denominator without a value: a key of score 0, or the head's learned score
+    const float extra = one_more ? 0.f : (shape.sinks != nullptr ? shape.sinks[h] : -CUDART_INF_F);
+    float M = extra;
     for (int w = 0; w < kWarps; ++w) M = fmaxf(M, m_s[w]);
-    float L = one_more ? expf(-M) : 0.f, f[kWarps];
+    float L = extra == -CUDART_INF_F ? 0.f : expf(extra - M), f[kWarps];
     for (int w = 0; w < kWarps; ++w) {
       f[w] = (m_s[w] == -CUDART_INF_F) ? 0.f : expf(m_s[w] - M);
       L += l_s[w] * f[w];
     }
     T* o = out + ((size_t)t * nq + h) * Dv;
+    const T* gate = shape.gate ? static_cast<const T*>(shape.gate) + (size_t)t * shape.gate_ld + (size_t)h * Dv : nullptr;
     for (int i = lane; i < Dv; i += 32) {
       float a = 0.f;
       for (int w = 0; w < kWarps; ++w) a += acc_s[w][i] * f[w];
-      o[i] = from_f32<T>(L > 0.f ? a / L * shape.out_scale : 0.f);
+      a = L > 0.f ? a / L * shape.out_scale : 0.f;
+      if (gate != nullptr) a *= 1.0f / (1.0f + expf(-to_f32(gate[i])));
+      o[i] = from_f32<T>(a);
     }
   }
 }
@@ -261,7 +266,7 @@ window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, co
   const int pos = positions[t];
   const int* table = block_table + (size_t)token_req[t] * max_pages;
   const int row_len = Dk + Dv;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_seen_key(pos, window, shape.chunk);
   const int keep = window > 0 ? keep_first : 0;
   const int keep_chunks = (keep + 31) / 32;
   const int lo_chunk = lo / 32;
@@ -374,19 +379,24 @@ window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, co
   __syncthreads();
   // warp g finishes head g: the warps' partial sums are merged in the order of the warps
   for (int g = warp; g < G; g += kGroupWarps) {
-    float M = one_more ? 0.f : -CUDART_INF_F;       // the one more key's score is 0
+    const int hq = hk * G + g;
+    const float extra = one_more ? 0.f : (shape.sinks != nullptr ? shape.sinks[hq] : -CUDART_INF_F);
+    float M = extra;
     for (int w = 0; w < kGroupWarps; ++w) M = fmaxf(M, m_s[w * GP + g]);
-    float L = one_more ? expf(-M) : 0.f, f[kGroupWarps];
+    float L = extra == -CUDART_INF_F ? 0.f : expf(extra - M), f[kGroupWarps];
     for (int w = 0; w < kGroupWarps; ++w) {
       const float mw = m_s[w * GP + g];
       f[w] = (mw == -CUDART_INF_F) ? 0.f : expf(mw - M);
       L += l_s[w * GP + g] * f[w];
     }
-    T* o = out + ((size_t)t * nq + hk * G + g) * Dv;
+    T* o = out + ((size_t)t * nq + hq) * Dv;
+    const T* gate = shape.gate ? static_cast<const T*>(shape.gate) + (size_t)t * shape.gate_ld + (size_t)hq * Dv : nullptr;
     for (int i = lane; i < Dv; i += 32) {
       float a = 0.f;
       for (int w = 0; w < kGroupWarps; ++w) a += acc_s[(w * GP + g) * Dv + i] * f[w];
-      o[i] = from_f32<T>(L > 0.f ? a / L * shape.out_scale : 0.f);
+      a = L > 0.f ? a / L * shape.out_scale : 0.f;
+      if (gate != nullptr) a *= 1.0f / (1.0f + expf(-to_f32(gate[i])));
+      o[i] = from_f32<T>(a);
     }
   }
 }
@@ -434,6 +444,7 @@ static int window_attention_any(const void* q, int q_row_stride, const void* pag
   if (T_ <= 0) return 0;
   if (Dk > kMaxDim || Dv > kMaxDim || Dk < 1 || Dv < 1 || nkv < 1 || nq % nkv || window < 0 || keep_first < 0)
     return KVB_ERR_BAD_SIZE;
+  if (shape.chunk < 0 || (shape.chunk > 0 && keep_first > 0) || (one_more && shape.sinks != nullptr)) return KVB_ERR_BAD_SIZE;
   const int esz = dtype == KVB_F32 ? 4 : 2;
   const int per16 = 16 / esz;
   const int vec = (Dk % per16 == 0 && (Dk + Dv) % per16 == 0 && ((uintptr_t)pages % 16) == 0) ? 1 : 0;
@@ -480,6 +491,149 @@ KVB_EXPORT int kvb_window_attention_shaped(const void* q, int q_row_stride, cons
   const ScoreShape shape = {head_scale, slopes, softcap, out_scale};
   return window_attention_any(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, positions, token_req,
                               out, T_, nq, nkv, Dk, Dv, scale, window, keep_first, one_more, shape, dtype, status, stream);
+}
+
+// The same with everything a ScoreShape can say: also a learned score per head in the denominator (sinks, float32
+// [nq] or null), a mask by blocks of `chunk` positions (0: none; not together with keep_first) and an output gate
+// (gate: activations' type, [T, >= nq * Dv] with row stride gate_ld, or null).
+KVB_EXPORT int kvb_window_attention_masked(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                           int max_pages, int page_size, int num_pages, const int* positions,
+                                           const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
+                                           float scale, int window, int keep_first, int one_more,
+                                           const float* head_scale, const float* slopes, float softcap, float out_scale,
+                                           const float* sinks, int chunk, const void* gate, int gate_ld, int dtype,
+                                           int* status, cudaStream_t stream) {
+  if (softcap < 0.f) return KVB_ERR_BAD_SIZE;
+  const ScoreShape shape = {head_scale, slopes, softcap, out_scale, sinks, chunk, gate, gate_ld};
+  return window_attention_any(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, positions, token_req,
+                              out, T_, nq, nkv, Dk, Dv, scale, window, keep_first, one_more, shape, dtype, status, stream);
+}
+
+// ---------------------------------------------------------------- biases, norms over the whole projection, rotation, cache write
+// src [T, ld] holds, per token, nq queries of Dk from column 0, nkv keys of Dk from k_off and nkv values of Dv from
+// v_off, as a product left them.  Each gets its bias (float32, may be null).  With qw (float32 [nq * Dk]) all of a
+// token's queries together are divided by their root mean square (eps inside the root) and multiplied by qw, before
+// they are cut into heads; the keys likewise with kw [nkv * Dk].  Then the first `rot` channels of every query and key
+// head turn by the token's position: channel pair i is (i, i + rot / 2) with layout 0 and (2 i, 2 i + 1) with layout
+// 1, and (u, v) becomes (u c - v s, v c + u s) with c = cos_t[pos][i], s = sin_t[pos][i] (float32 tables of
+// table_len rows, rot / 2 wide; any factor on the rotation is in the tables).  Queries go to q_out [T, nq * Dk];
+// keys and values into the request's pages, a row [key | value] per token and key/value head.  One block per token;
+// the token's queries and keys wait in shared memory as float32 between the steps.
+struct QkRotArgs {
+  const void* src; int ld, k_off, v_off;
+  const float* bq; const float* bk; const float* bv;
+  const float* qw; const float* kw; float eps;
+  const float* cos_t; const float* sin_t; int table_len, rot, layout;
+  void* q_out; void* pages;
+  const int* block_table; int max_pages, page_size, num_pages;
+  const int* positions; const int* token_req;
+  int nq, nkv, Dk, Dv, write;
+  int* status;
+};
+
+__device__ __forceinline__ float turned(const float* x, int d, int rot, int layout, const float* c, const float* s) {
+  if (d >= rot) return x[d];
+  const int half = rot >> 1;
+  if (layout == 0) {
+    return d < half ? x[d] * c[d] - x[d + half] * s[d] : x[d] * c[d - half] + x[d - half] * s[d - half];
+  }
+  const int i = d >> 1;
+  return (d & 1) == 0 ? x[d] * c[i] - x[d + 1] * s[i] : x[d] * c[i] + x[d - 1] * s[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_rot_append_kernel(QkRotArgs a) {
+  extern __shared__ float qk_s[];             // [nq * Dk] queries, then [nkv * Dk] keys
+  __shared__ float part[2][8];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nQ = a.nq * a.Dk, nK = a.nkv * a.Dk, nV = a.nkv * a.Dv;
+  float* ks = qk_s + nQ;
+  const T* row = static_cast<const T*>(a.src) + (size_t)t * a.ld;
+  const int pos = a.positions[t];
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nQ; i += blockDim.x) {
+    const float v = to_f32(row[i]) + (a.bq ? a.bq[i] : 0.f);
+    qk_s[i] = v;
+    sq = fmaf(v, v, sq);
+  }
+  for (int i = threadIdx.x; i < nK; i += blockDim.x) {
+    const float v = to_f32(row[a.k_off + i]) + (a.bk ? a.bk[i] : 0.f);
+    ks[i] = v;
+    sk = fmaf(v, v, sk);
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) { part[0][warp] = sq; part[1][warp] = sk; }
+  __syncthreads();
+  float tq = 0.f, tk = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { tq += part[0][w]; tk += part[1][w]; }
+  if (a.qw != nullptr) {
+    const float r = 1.0f / sqrtf(tq / (float)nQ + a.eps);
+    for (int i = threadIdx.x; i < nQ; i += blockDim.x) qk_s[i] = qk_s[i] * r * a.qw[i];
+  }
+  if (a.kw != nullptr) {
+    const float r = 1.0f / sqrtf(tk / (float)nK + a.eps);
+    for (int i = threadIdx.x; i < nK; i += blockDim.x) ks[i] = ks[i] * r * a.kw[i];
+  }
+  __syncthreads();
+  int rot = a.rot;
+  const float* c = nullptr;
+  const float* s = nullptr;
+  if (rot > 0) {
+    if (pos < 0 || pos >= a.table_len) {
+      if (threadIdx.x == 0) atomicCAS(a.status, 0, KVB_STATUS_BAD_POSITION);
+      rot = 0;
+    } else {
+      c = a.cos_t + (size_t)pos * (a.rot >> 1);
+      s = a.sin_t + (size_t)pos * (a.rot >> 1);
+    }
+  }
+  T* q_out = static_cast<T*>(a.q_out) + (size_t)t * nQ;
+  for (int i = threadIdx.x; i < nQ; i += blockDim.x) {
+    const int head = i / a.Dk, d = i - head * a.Dk;
+    q_out[i] = from_f32<T>(turned(qk_s + head * a.Dk, d, rot, a.layout, c, s));
+  }
+  if (!a.write) return;
+  const int lp = pos / a.page_size;
+  const int page = (pos >= 0 && lp < a.max_pages) ? a.block_table[(size_t)a.token_req[t] * a.max_pages + lp] : -1;
+  if (page < 0 || page >= a.num_pages) {
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, KVB_STATUS_UNMAPPED_PAGE);
+    return;
+  }
+  T* pages = static_cast<T*>(a.pages);
+  const int row_len = a.Dk + a.Dv;
+  for (int i = threadIdx.x; i < nK; i += blockDim.x) {
+    const int head = i / a.Dk, d = i - head * a.Dk;
+    pages[(((size_t)page * a.nkv + head) * a.page_size + (pos % a.page_size)) * row_len + d] =
+        from_f32<T>(turned(ks + head * a.Dk, d, rot, a.layout, c, s));
+  }
+  for (int i = threadIdx.x; i < nV; i += blockDim.x) {
+    const int head = i / a.Dv, d = i - head * a.Dv;
+    pages[(((size_t)page * a.nkv + head) * a.page_size + (pos % a.page_size)) * row_len + a.Dk + d] =
+        from_f32<T>(to_f32(row[a.v_off + i]) + (a.bv ? a.bv[i] : 0.f));
+  }
+}
+
+// Refuses: head sizes above 256, rot odd or above Dk, a layout other than 0 or 1, more than 48 K queries and keys a token.
+KVB_EXPORT int kvb_qk_rot_append(const QkRotArgs* args, int T_, int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  const QkRotArgs a = *args;
+  if (a.Dk > kMaxDim || a.Dv > kMaxDim || a.Dk < 1 || a.Dv < 1 || a.nkv < 1 || a.nq < 1) return KVB_ERR_BAD_SIZE;
+  if (a.rot < 0 || a.rot > a.Dk || (a.rot & 1) || a.layout < 0 || a.layout > 1) return KVB_ERR_BAD_SIZE;
+  if (a.rot > 0 && (a.cos_t == nullptr || a.sin_t == nullptr)) return KVB_ERR_BAD_SIZE;
+  const size_t smem = (size_t)(a.nq + a.nkv) * a.Dk * sizeof(float);
+  if (smem > 192 * 1024) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(qk_rot_append_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    kvb_launch(qk_rot_append_kernel<T>, dim3(T_), dim3(256), smem, stream, a);
+  });
+  return kvb_launch_result();
 }
 
 // ---------------------------------------------------------------- biases, per-head norms and the cache write

@@ -201,8 +201,8 @@ def _need_cuda(*ts):
 # ------------------------------------------------------------------ elementwise
 
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
-                 sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 residual rows ``table[ids]``.  With ``sampled`` (int32), an id ``-(1 + r)``
+                 sampled: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """float32 residual rows ``table[ids] * scale`` (the factor applied in float32).  With ``sampled`` (int32), an id ``-(1 + r)``
     stands for ``sampled[r]``: a token that is still on the device."""
     _need_cuda(table, ids, sampled)
     assert sampled is None or (sampled.dtype == torch.int32 and sampled.is_contiguous())
@@ -211,7 +211,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
     out = new((T, H), torch.float32, table.device)
     rc = lib("elementwise").kvb_embed_gather(_p(table), dtype_code(table.dtype), _p(ids), _p(sampled),
                                              c_int(0 if sampled is None else sampled.numel()), _p(out),
-                                             c_int(T), c_int(H), c_int(V), _p(status), _stream())
+                                             c_int(T), c_int(H), c_int(V), c_float(scale), _p(status), _stream())
     _check(rc, "embed_gather")
     return out
 
@@ -271,7 +271,7 @@ def rope_kv_write(qkv, positions, token_req, cos, sin, k_pages, v_pages, block_t
 
 # ------------------------------------------------------------------ norms around a branch, gated activations
 
-NORM_KINDS = {None: 0, "none": 0, "layer": 1, "rms": 2}
+NORM_KINDS = {None: 0, "none": 0, "copy": 0, "layer": 1, "rms": 2}
 
 
 class PostNormed:
@@ -297,7 +297,8 @@ def add_norm(resid: torch.Tensor, pending, kind: Optional[str], weight: Optional
     """``resid += post(pending)`` in float32 (in place unless ``rows`` selects), then the norm
     ``kind`` ("layer": (v - mean) / sqrt(var + eps), "rms": v / sqrt(mean(v^2) + eps)) of the sum
     times ``weight``.  ``pending``: None, a tensor [T, H] that is added as it is, or a
-    :class:`PostNormed`.  ``kind`` None: only the residual is brought up to date."""
+    :class:`PostNormed`.  ``kind`` None: only the residual is brought up to date; "copy": the sum itself comes back
+    in ``out_dtype`` (for a sublayer that reads the stream without a norm in front)."""
     _need_cuda(resid)
     assert resid.dtype == torch.float32 and resid.is_contiguous()
     T, H = resid.shape
@@ -333,6 +334,15 @@ def bias_act_mul(gate_up: torch.Tensor, bias: Optional[torch.Tensor], act: str) 
                                          c_int(ACT_KINDS[act]), c_int(dtype_code(gate_up.dtype)), _stream())
     _check(rc, "bias_act_mul")
     return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """``x <- cap * tanh(x * scale / cap)`` in place on a float32 tensor (``cap`` 0: only the factor)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    rc = lib("rowwise").kvb_scale_softcap(_p(x), ctypes.c_size_t(x.numel()), c_float(scale), c_float(cap), _stream())
+    _check(rc, "scale_softcap")
+    return x
 
 
 def tanh_slice(x: torch.Tensor, first: int, n: int) -> torch.Tensor:
@@ -681,18 +691,41 @@ def kv_rows_append(src: torch.Tensor, k_off: int, v_off: int, pages: torch.Tenso
 def window_attention(q: torch.Tensor, q_off: int, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int,
                      dk: int, dv: int, scale: float, window: int, keep_first: int, one_more: bool,
                      head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
-                     softcap: float = 0.0, out_scale: float = 1.0) -> torch.Tensor:
+                     softcap: float = 0.0, out_scale: float = 1.0, sinks: Optional[torch.Tensor] = None,
+                     chunk: int = 0, gate=None) -> torch.Tensor:
     """Attention of every token (queries at ``q[:, q_off : q_off + heads * dk]``) over its request's cached
     rows [key | value]: query i sees key j when ``j <= i and (i - j < window or j < keep_first)`` (``window``
     0: every key up to i); ``one_more``: the softmax's denominator is ``1 + sum exp(s)``.  Positions do
     not enter the scores unless ``slopes`` is given.  On its way to the softmax a score ``(q . k) * scale`` is
     multiplied by ``head_scale[h]`` (float32 [heads]), capped as ``softcap * tanh(s / softcap)`` (``softcap`` 0: not),
     and lowered by ``slopes[h] * (i - j)`` (float32 [heads]); the result is multiplied by ``out_scale``.
+    ``sinks`` (float32 [heads]): ``exp(sinks[h])`` joins the softmax's denominator once, without a value.  ``chunk`` > 0:
+    query i sees key j <= i only when ``i // chunk == j // chunk``, blocks counted from the sequence's start.
+    ``gate``: (tensor, first column) of rows in the activations' type by whose sigmoid the result is multiplied.
     Returns [T, heads * dv]."""
     _need_cuda(q, pages)
     assert q.stride(1) == 1 and pages.is_contiguous() and pages.dtype == q.dtype
     T = q.shape[0]
     out = new((T, heads * dv), q.dtype, q.device)
+    if sinks is not None or chunk or gate is not None:
+        for v in (head_scale, slopes, sinks):
+            assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
+        gate_at, gate_ld = 0, 0
+        if gate is not None:
+            gt, gcol = gate
+            assert gt.dtype == q.dtype and gt.stride(1) == 1 and gt.shape[0] == T and gt.shape[1] >= gcol + heads * dv
+            gate_at, gate_ld = _at(gt, gcol), gt.stride(0)
+        rc = lib("window_attention").kvb_window_attention_masked(
+            c_void_p(_at(q, q_off)), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+            c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions), _p(batch.token_req), _p(out), c_int(T),
+            c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_float(scale), c_int(int(window or 0)),
+            c_int(int(keep_first or 0)), c_int(1 if one_more else 0), _p(head_scale), _p(slopes), c_float(float(softcap or 0.0)),
+            c_float(float(out_scale)), _p(sinks), c_int(int(chunk or 0)), c_void_p(gate_at), c_int(gate_ld),
+            c_int(dtype_code(q.dtype)), _p(batch.status), _stream())
+        _check(rc, "window_attention")
+        choices["window_attention"] += 1
+        choices["window_attention_masked"] += 1
+        return out
     if head_scale is not None or slopes is not None or softcap or out_scale != 1.0:
         for v in (head_scale, slopes):
             assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
@@ -784,6 +817,49 @@ def qk_norm_append(p: torch.Tensor, first: int, k_off: int, v_off: int, bq, bk, 
         _p(batch.positions), _p(batch.token_req), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
         c_int(1 if write else 0), c_int(dtype_code(p.dtype)), _p(batch.status), _stream())
     _check(rc, "qk_norm_append")
+    return q
+
+
+class _QkRotArgs(ctypes.Structure):
+    _fields_ = [("src", c_void_p), ("ld", c_int), ("k_off", c_int), ("v_off", c_int), ("bq", c_void_p), ("bk", c_void_p),
+                ("bv", c_void_p), ("qw", c_void_p), ("kw", c_void_p), ("eps", c_float), ("cos_t", c_void_p),
+                ("sin_t", c_void_p), ("table_len", c_int), ("rot", c_int), ("layout", c_int), ("q_out", c_void_p),
+                ("pages", c_void_p), ("block_table", c_void_p), ("max_pages", c_int), ("page_size", c_int),
+                ("num_pages", c_int), ("positions", c_void_p), ("token_req", c_void_p), ("nq", c_int), ("nkv", c_int),
+                ("Dk", c_int), ("Dv", c_int), ("write", c_int), ("status", c_void_p)]
+
+
+ROTARY_LAYOUTS = {"half": 0, "pairs": 1}
+
+
+def qk_rot_append(p: torch.Tensor, first: int, k_off: int, v_off: int, bq, bk, bv, qw, kw, eps: float, cos, sin,
+                  rot: int, layout: str, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int, dk: int,
+                  dv: int, write: bool = True) -> torch.Tensor:
+    """From a product's rows to queries and cached rows.  ``p[:, first:]`` holds a token's ``heads`` queries of
+    ``dk``, its ``kv_heads`` keys ``k_off`` columns further and its values ``v_off`` columns further.  Each gets its
+    bias (float32 or None); with ``qw`` (float32 [heads * dk]) all queries of a token together are divided by their
+    root mean square (``eps`` inside the root) and multiplied by ``qw``, likewise the keys with ``kw``; then the
+    first ``rot`` channels of every query and key head turn by the token's position (``cos``, ``sin``: float32
+    [positions, rot / 2]; ``layout`` "half": pair (i, i + rot / 2), "pairs": (2 i, 2 i + 1)).  Keys and values go
+    into the request's pages as rows [key | value].  Returns the queries [T, heads * dk]."""
+    _need_cuda(p, pages)
+    assert p.stride(1) == 1 and pages.is_contiguous() and pages.dtype == p.dtype
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
+    for v, n in ((bq, heads * dk), (bk, kv_heads * dk), (bv, kv_heads * dv), (qw, heads * dk), (kw, kv_heads * dk)):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n)
+    table_len = 0
+    if rot:
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == rot // 2
+        table_len = cos.shape[0]
+    T = p.shape[0]
+    q = new((T, heads * dk), p.dtype, p.device)
+    a = _QkRotArgs(_at(p, first), p.stride(0), k_off, v_off, *(0 if v is None else v.data_ptr() for v in (bq, bk, bv, qw, kw)),
+                   float(eps), cos.data_ptr() if rot else 0, sin.data_ptr() if rot else 0, table_len, int(rot),
+                   ROTARY_LAYOUTS[layout], q.data_ptr(), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                   pages.shape[2], pages.shape[0], batch.positions.data_ptr(), batch.token_req.data_ptr(), heads, kv_heads,
+                   dk, dv, 1 if write else 0, batch.status.data_ptr())
+    rc = lib("window_attention").kvb_qk_rot_append(ctypes.byref(a), c_int(T), c_int(dtype_code(p.dtype)), _stream())
+    _check(rc, "qk_rot_append")
     return q
 
 
@@ -1109,6 +1185,79 @@ def ssd_scan(xbc: torch.Tensor, dt, dt_bias: torch.Tensor, a_log: torch.Tensor, 
     return y
 
 
+class _MlstmArgs(ctypes.Structure):
+    _fields_ = [("qkv", c_void_p), ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int),
+                ("gates", c_void_p), ("ld_g", c_int), ("bi", c_void_p), ("bf", c_void_p), ("cap", c_float),
+                ("q_scale", c_float), ("state", c_void_p), ("slot_stride", c_longlong), ("y", c_void_p),
+                ("q_start", c_void_p), ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("N", c_int),
+                ("Dv", c_int), ("chunk", c_int), ("row_off", c_int), ("local", c_void_p), ("carry", c_void_p),
+                ("fsum", c_void_p)]
+
+
+def mlstm_state_floats(heads: int, n: int, dv: int) -> int:
+    """float32 numbers of one request's state of :func:`mlstm_scan`: the matrices [heads, dv, n], then the vector n
+    and the maximum m once per block of 64 value columns."""
+    splits = -(-dv // 64)
+    return heads * dv * n + heads * splits * (n + 1)
+
+
+def mlstm_scan(p: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, bi: torch.Tensor,
+               bf: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor, batch, heads: int, n: int,
+               dv: int) -> torch.Tensor:
+    """A matrix memory ``C`` [n, dv] per head with exponential gates and a running maximum ``m``, along every
+    request's tokens of the step::
+
+        i = cap tanh((a + bi) / cap),  f = logsigmoid(cap tanh((b + bf) / cap)),  m' = max(f + m, i)
+        C <- exp(f + m - m') C + exp(i - m') k v^T,  n <- (likewise with k),  y = C^T q / (max(|n . q|, exp(-m')) + 1e-6)
+
+    ``p`` [T, ...] holds q (``heads * n`` from column ``q_off``; multiplied by ``q_scale``), k and v; ``gates`` float32
+    [T, 2 heads]: the raw a, then the raw b.  ``state``: float32 [slots, >= mlstm_state_floats], empty (m = 0) for a
+    request that starts at position 0.  Returns float32 y [T, heads * dv].  A step with a run of
+    ``SCAN_CHUNK_MIN_RUN`` tokens or more walks chunks of 64 tokens side by side."""
+    _need_cuda(p, gates, state)
+    T = p.shape[0]
+    assert p.stride(1) == 1 and gates.dtype == torch.float32 and gates.stride(1) == 1 and gates.shape[1] >= 2 * heads
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= mlstm_state_floats(heads, n, dv)
+    for v in (bi, bf):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
+    y = new((T, heads * dv), torch.float32, p.device)
+    max_run = int(getattr(batch, "max_q_len", 0) or 0)
+    chunk = first = local = carry = fsum = 0
+    if max_run >= SCAN_CHUNK_MIN_RUN and not _capturing():
+        chunk = 64
+        rows, first = _chunk_rows(batch, chunk)
+        per = mlstm_state_floats(heads, n, dv)
+        mats = new((2, rows, per), torch.float32, p.device)
+        fsum_t = new((rows, heads), torch.float32, p.device)
+        local, carry, fsum = mats[0].data_ptr(), mats[1].data_ptr(), fsum_t.data_ptr()
+        choices["mlstm_scan_chunked"] += 1
+    a = _MlstmArgs(p.data_ptr(), p.stride(0), q_off, k_off, v_off, gates.data_ptr(), gates.stride(0),
+                   0 if bi is None else bi.data_ptr(), 0 if bf is None else bf.data_ptr(), float(cap), float(q_scale),
+                   state.data_ptr(), state.stride(0), y.data_ptr(), batch.q_start.data_ptr(), batch.req_start.data_ptr(),
+                   batch.slots.data_ptr(), heads, n, dv, chunk, first, local, carry, fsum)
+    rc = lib("mlstm").kvb_mlstm_scan(ctypes.byref(a), c_int(batch.num_reqs), c_int(max_run), c_int(dtype_code(p.dtype)),
+                                     _stream())
+    _check(rc, "mlstm_scan")
+    return y
+
+
+def head_norm_gate(y: torch.Tensor, gate, weight: torch.Tensor, heads: int, eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Every head of ``y`` (float32 [T, heads * dv]) divided by its own root mean square (eps inside the root), times
+    ``weight`` (float32 [heads * dv]), times the sigmoid of ``gate``: (tensor, first column), compute type."""
+    _need_cuda(y, weight)
+    T, width = y.shape
+    gt, gcol = gate
+    assert y.dtype == torch.float32 and y.is_contiguous() and gt.stride(1) == 1 and gt.dtype == out_dtype
+    assert weight.dtype == torch.float32 and weight.numel() == width and width % heads == 0
+    out = new((T, width), out_dtype, y.device)
+    rc = lib("mlstm").kvb_head_norm_gate(_p(y), c_void_p(_at(gt, gcol)), c_int(gt.stride(0)), _p(weight), _p(out),
+                                         c_int(T), c_int(heads), c_int(width // heads), c_float(eps),
+                                         c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "head_norm_gate")
+    return out
+
+
 def gated_group_norm(y: torch.Tensor, z, weight: torch.Tensor, groups: int, eps: float,
                      out_dtype: torch.dtype) -> torch.Tensor:
     """``v = y * silu(z)``, then each of ``groups`` equal parts of a row divided by its own root mean square (eps
@@ -1128,24 +1277,33 @@ def gated_group_norm(y: torch.Tensor, z, weight: torch.Tensor, groups: int, eps:
 
 # ------------------------------------------------------------------ routed experts
 
-def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, experts: int, identity: int, top: int,
-          scale: float, logits: Optional[torch.Tensor] = None):
+def route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], experts: int, identity: int, top: int,
+          scale: float, logits: Optional[torch.Tensor] = None, score: str = "softmax", renormalize: bool = True):
     """The router of a feed-forward of many experts.  ``w_router`` float32 [experts + identity, K],
     ``correction`` float32 [experts + identity] (added to the scores for the choice only).  Returns
     ``gate`` float32 [T, experts + identity], a token's weight for every expert (0 where not chosen), and
     float32 [T], the summed weights of its identity experts (None without any).  ``logits``: float32
     [T, experts + identity], the products ``h . w_router^T`` if the caller has made them already (by a matrix
-    product that adds up in float32), in which case the kernel only chooses."""
+    product that adds up in float32; further columns behind them are left alone), in which case the kernel only
+    chooses.  ``score`` "softmax": the scores are the logits' softmax over all experts; "sigmoid": each logit's sigmoid.
+    ``renormalize`` False: a chosen expert's weight is its score times ``scale``, not divided by the chosen scores' sum.
+    ``correction`` None: the choice goes by the scores alone."""
     _need_cuda(h, w_router)
     T, K = h.shape
     n_all = experts + identity
-    assert w_router.dtype == torch.float32 and w_router.is_contiguous() and tuple(w_router.shape) == (n_all, K)
-    assert correction.dtype == torch.float32 and correction.numel() == n_all and h.stride(1) == 1
-    assert logits is None or (logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, n_all))
+    assert logits is not None or w_router is not None
+    assert w_router is None or (w_router.dtype == torch.float32 and w_router.is_contiguous()
+                                and tuple(w_router.shape) == (n_all, K))
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_all)
+    assert h.stride(1) == 1
+    assert logits is None or (logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[0] == T
+                              and logits.shape[1] >= n_all)
     gate = new((T, n_all), torch.float32, h.device)
     idw = new((T,), torch.float32, h.device) if identity else None
-    rc = lib("experts").kvb_route(_p(h), c_int(h.stride(0)), _p(w_router), _p(logits), _p(correction), _p(gate), _p(idw), c_int(T),
+    rc = lib("experts").kvb_route(_p(h), c_int(h.stride(0)), _p(w_router), _p(logits),
+                                  c_int(0 if logits is None else logits.stride(0)), _p(correction), _p(gate), _p(idw), c_int(T),
                                   c_int(K), c_int(experts), c_int(identity), c_int(top), c_float(scale),
+                                  c_int({"softmax": 0, "sigmoid": 1}[score]), c_int(1 if renormalize else 0),
                                   c_int(dtype_code(h.dtype)), _stream())
     _check(rc, "route")
     return gate, idw
@@ -1160,6 +1318,27 @@ def expert_act(p: torch.Tensor, gate: torch.Tensor, experts: int, ff: int, share
     rc = lib("experts").kvb_expert_act(_p(p), _p(gate), c_int(gate.stride(0)), _p(out), c_int(p.shape[0]), c_int(experts),
                                        c_int(ff), c_int(shared_ff), c_int(dtype_code(p.dtype)), _stream())
     _check(rc, "expert_act")
+    return out
+
+
+def limited_act(p: torch.Tensor, gate: torch.Tensor, shared_logit: Optional[torch.Tensor], experts: int, ff: int,
+                shared_ff: int, pad: int, limit: float, shared_limit: float, alpha: float) -> torch.Tensor:
+    """The activation of experts ``down(a(g) (u + 1))`` with ``g = min(w gate.h, limit)``, ``u = clamp(w up.h, +-limit)``,
+    ``a(g) = g sigmoid(alpha g)`` and ``w`` the token's weight for the expert (``gate`` float32 [T, >= experts], 0 where
+    not chosen).  ``p`` [T, 2 (experts ff + shared_ff)]: per expert its gate product, then its up product; behind
+    them those of an expert that every token uses, whose result is multiplied by ``sigmoid(shared_logit[t])`` (float32
+    column, may be a strided view; None: by 1).  Returns [T, experts ff + shared_ff + pad], the padding zero."""
+    _need_cuda(p, gate)
+    assert p.stride(1) == 1 and gate.dtype == torch.float32 and gate.stride(1) == 1
+    assert shared_logit is None or (shared_logit.dtype == torch.float32 and shared_logit.shape[0] == p.shape[0])
+    width = experts * ff + shared_ff + pad
+    out = new((p.shape[0], width), p.dtype, p.device)
+    rc = lib("experts").kvb_limited_act(_p(p), c_int(p.stride(0)), _p(gate), c_int(gate.stride(0)), _p(shared_logit),
+                                        c_int(0 if shared_logit is None else shared_logit.stride(0)), _p(out),
+                                        c_int(p.shape[0]), c_int(experts), c_int(ff), c_int(shared_ff), c_int(pad),
+                                        c_float(limit), c_float(shared_limit), c_float(alpha), c_int(dtype_code(p.dtype)),
+                                        _stream())
+    _check(rc, "limited_act")
     return out
 
 

@@ -95,6 +95,44 @@ class SandwichMixerBlock(SandwichBlock):
     part_families = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm"}
 
 
+@register("block", "postnorm")
+class PostNormBlock(Part):
+    """``h += post1(mixer(h)); h += post2(ff(h))``: the sublayers read the residual stream itself, and only their
+    outputs pass a norm (whose weight carries any constant on the branch) before they join it.  A branch output
+    travels on as an :class:`ops.PostNormed`; the kernel that norms it and adds it to the float32 stream also leaves
+    the copy of the new stream in the compute type that the next sublayer reads (``ops.add_norm`` with "copy"), so a
+    sublayer boundary is one launch, as in the arrangements with a norm in front."""
+
+    part_families = {"mixer": "mixer", "mixer_post_norm": "norm", "feed_forward": "feed_forward", "ff_post_norm": "norm"}
+
+    def __init__(self, parts):
+        self.parts = dict(parts)
+        self.mixer, self.mixer_post = parts["mixer"], parts["mixer_post_norm"]
+        self.feed_forward, self.ff_post = parts.get("feed_forward"), parts.get("ff_post_norm")
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, residual, delta, batch, cache):
+        dtype = self.mixer.ctx.dtype
+        x = ops.add_norm(residual, delta, "copy", None, 0.0, dtype)
+        if getattr(self.mixer, "hands_over_bias", False):      # the last product's bias rides with the pending output
+            pending = self.mixer_post.as_pending(*self.mixer.forward(x, batch, cache, bias_out=True))
+        else:
+            pending = self.mixer_post.as_pending(self.mixer.forward(x, batch, cache))
+        if self.feed_forward is None:
+            return residual, pending
+        x = ops.add_norm(residual, pending, "copy", None, 0.0, dtype)
+        return residual, self.ff_post.as_pending(self.feed_forward.forward(x, batch))
+
+
+@register("block", "postnorm_mixer_only")
+class PostNormMixerBlock(PostNormBlock):
+    """The post-norm block of a layer that has no feed-forward: ``h += post1(mixer(h))``."""
+
+    part_families = {"mixer": "mixer", "mixer_post_norm": "norm"}
+
+
 @register("block", "parallel")
 class ParallelBlock(Part):
     """``h += mixer(norm(h)) + ff(norm(h))``: one norm, whose output both sublayers read.  The two

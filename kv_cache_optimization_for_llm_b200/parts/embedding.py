@@ -10,8 +10,9 @@ from .registry import register
 
 @register("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """``residual[t] = table[token[t]]``, no scaling (upstream: base/src/kernels.cu:279-287).
-    The residual stream starts, and stays, in float32.  params: vocab_size, hidden_size."""
+    """``residual[t] = table[token[t]] * scale`` (upstream, without a factor: base/src/kernels.cu:279-287).
+    The residual stream starts, and stays, in float32; the factor is applied there.
+    params: vocab_size, hidden_size, scale (1 when absent)."""
 
     @classmethod
     def weight_specs(cls, params):
@@ -24,9 +25,10 @@ class TokenEmbedding(Part):
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
         self.table = weights["table"]
+        self.scale = float(params.get("scale", 1.0) or 1.0)
 
     def forward(self, batch):
-        return ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled)
+        return ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled, self.scale)
 
 
 @register("embedding", "normed_token_embedding")
@@ -49,7 +51,7 @@ class NormedTokenEmbedding(TokenEmbedding):
 
     def forward(self, batch):
         import torch
-        rows = ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled)
+        rows = ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled, self.scale)
         return ops.join_norm(rows, None, "rms", self.norm_weight, self.eps, torch.float32, compute_dtype=self.ctx.dtype)
 
 
@@ -57,7 +59,9 @@ class NormedTokenEmbedding(TokenEmbedding):
 class LinearHead(Part):
     """``logits = x . W^T`` in float32 output, W either its own tensor or the embedding
     table when tied (upstream: base/src/engine.cu:872-890, always tied, bfloat16
-    logits).  params: vocab_size, hidden_size."""
+    logits).  With ``scale`` and ``softcap`` the logits become ``softcap * tanh(logits * scale / softcap)``
+    (``softcap`` absent or 0: only the factor), in float32, in place.
+    params: vocab_size, hidden_size, scale, softcap."""
 
     @classmethod
     def weight_specs(cls, params):
@@ -66,15 +70,21 @@ class LinearHead(Part):
     @classmethod
     def kernel_modules(cls, params, dtype):
         import torch
-        return ("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide")
+        shaped = ("rowwise",) if (params.get("softcap") or float(params.get("scale", 1.0) or 1.0) != 1.0) else ()
+        return shaped + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
         self.weight = weights["weight"]
+        self.scale = float(params.get("scale", 1.0) or 1.0)
+        self.softcap = float(params.get("softcap") or 0.0)
 
     def forward(self, x):
         import torch
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        if self.softcap or self.scale != 1.0:
+            ops.scale_softcap(logits, self.scale, self.softcap)
+        return logits
 
 
 @register("embedding", "sinusoid_stream_embedding")

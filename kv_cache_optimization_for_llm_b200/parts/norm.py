@@ -13,7 +13,12 @@ class RMSNorm(Part):
     """``y = v / sqrt(mean(v^2) + eps) * w`` over the whole width, plain weight
     (upstream: base/src/kernels.cu:10-36), where ``v = residual + delta`` is summed
     and kept in float32 (upstream adds in a second kernel and keeps bfloat16,
-    base/src/kernels.cu:38-43).  params: size, eps."""
+    base/src/kernels.cu:38-43).  With ``scale`` (a constant on a branch, or on the logits behind the model's last
+    norm) the weight is multiplied by it once, when the model is built.
+
+    The same part may stand behind a branch (``as_pending``): there it is not carried out at once but handed on as
+    an :class:`ops.PostNormed`, and whoever brings the residual stream up to date next norms the branch output and
+    adds it in one kernel.  params: size, eps, scale."""
 
     @classmethod
     def weight_specs(cls, params):
@@ -28,9 +33,15 @@ class RMSNorm(Part):
         self.eps = float(params["eps"])
         self.size = int(params["size"])
         self.weight = weights["weight"]
+        if params.get("scale") is not None and float(params["scale"]) != 1.0:
+            self.weight = (self.weight * float(params["scale"])).contiguous()
 
     def activation_widths(self):
         return [self.size]
+
+    def as_pending(self, delta, bias=None):
+        """``delta`` (a branch's output, ``bias`` still to be added) with this norm pending on it."""
+        return ops.PostNormed(delta, bias, "rms", self.weight, self.eps)
 
     def give_up_weight(self):
         """Hands the weight to a part that multiplies it into its own matrices

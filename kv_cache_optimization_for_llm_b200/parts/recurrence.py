@@ -1,10 +1,11 @@
 """Mixers whose state is a linear recurrence with a decay that depends on the token: a gated diagonal
-recurrence per channel, and a matrix state per head with one decay per head (state-space duality).
+recurrence per channel, a matrix state per head with one decay per head (state-space duality), and a matrix
+memory per head with exponential gates and a running maximum (mLSTM).
 
-Both make their projections in one product, pass part of it through a short causal convolution whose last
+The first two make their projections in one product, pass part of it through a short causal convolution whose last
 inputs live in the request's state slot beside the recurrence's state (float32), and walk the request's
-tokens of the step in one kernel (csrc/kernels/recurrence.cu).  A request that starts at position 0 starts
-from a zero state.
+tokens of the step in one kernel (csrc/kernels/recurrence.cu); the third has no convolution and its kernels are
+csrc/kernels/mlstm.cu.  A request that starts at position 0 starts from a zero state.
 """
 
 from __future__ import annotations
@@ -151,3 +152,61 @@ class StateSpaceDuality(Part):
                          self.N, self.Dv)
         g = ops.gated_group_norm(y, (p, self.at_z), self.norm, self.norm_groups, self.eps, self.ctx.dtype)
         return ops.linear(g, self.o)
+
+
+@register("mixer", "mlstm")
+class MatrixLSTM(Part):
+    """A matrix memory per head with exponential gates (the mLSTM cell of xLSTM).  One product lays out
+    [q: heads * dim | k: heads * dim | v: heads * vdim | g: heads * vdim]; a second, with float32 results, makes the raw
+    gates [a: heads | b: heads].  Per head, with ``q`` multiplied by ``dim^(-1/2)``,
+    ``i = cap tanh((a + b_i) / cap)`` and ``f = logsigmoid(cap tanh((b + b_f) / cap))``, and a running maximum ``m``:
+
+        m_t = max(f + m_{t-1}, i),    C_t = exp(f + m_{t-1} - m_t) C_{t-1} + exp(i - m_t) k v^T    (C is dim x vdim),
+        n_t likewise with k alone,     y_t = C_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6),
+
+    from C = 0, n = 0, m = 0.  Every head's y is divided by its own root mean square (``eps`` inside the root); the
+    heads, side by side, are multiplied by ``norm``, by ``sigmoid(g)``, and projected by W_o.  Gates, exponentials and
+    the state are float32; the request's state slot holds C, n and m.
+    params: hidden_size, heads, dim, vdim, gate_cap, eps."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, H, D, Dv = (int(params[k]) for k in ("hidden_size", "heads", "dim", "vdim"))
+        return {"q": WeightSpec((H * D, h)), "k": WeightSpec((H * D, h)), "v": WeightSpec((H * Dv, h)),
+                "g": WeightSpec((H * Dv, h)), "i": WeightSpec((H, h)), "f": WeightSpec((H, h)),
+                "i_bias": WeightSpec((H,), "bias"), "f_bias": WeightSpec((H,), "bias"),
+                "norm": WeightSpec((H * Dv,), "vector"), "o": WeightSpec((h, H * Dv))}
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("mlstm",) + _gemm_modules(dtype)
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.H, self.D, self.Dv = (int(params[k]) for k in ("heads", "dim", "vdim"))
+        self.cap, self.eps = float(params["gate_cap"]), float(params["eps"])
+        if not 1 <= self.D <= 256:
+            raise ValueError(f"mlstm: keys of {self.D} channels are refused (1 to 256)")
+        if not self.cap > 0:
+            raise ValueError(f"mlstm: a gate cap of {self.cap} is refused (above zero)")
+        self.w_in, (self.at_q, self.at_k, self.at_v, self.at_g) = _stack(
+            [weights["q"], weights["k"], weights["v"], weights["g"]], ctx.dtype)
+        # the raw gates are float32 sums: their matrix stays apart from the others
+        self.w_gates = torch.cat([weights["i"], weights["f"]], dim=0).contiguous()
+        self.i_bias, self.f_bias = weights["i_bias"], weights["f_bias"]
+        self.norm, self.o = weights["norm"], weights["o"]
+        self.state_floats = ops.mlstm_state_floats(self.H, self.D, self.Dv)
+
+    def cache_spec(self):
+        return SlotStateSpec((self.state_floats,), torch.float32)
+
+    def activation_widths(self):
+        inner = self.H * self.Dv
+        return [self.w_in.shape[0], 2 * (2 * self.H + 8), 2 * inner, inner, self.o.shape[0]]
+
+    def forward(self, x, batch, cache):
+        p = ops.linear(x, self.w_in)
+        gates = ops.linear(x, self.w_gates, out_dtype=torch.float32)
+        y = ops.mlstm_scan(p, self.at_q, self.at_k, self.at_v, gates, self.i_bias, self.f_bias, self.cap,
+                           self.D ** -0.5, cache.state, batch, self.H, self.D, self.Dv)
+        return ops.linear(ops.head_norm_gate(y, (p, self.at_g), self.norm, self.H, self.eps, self.ctx.dtype), self.o)

@@ -1,7 +1,8 @@
 """Attention over a sliding window with one row [key | value] per token and key/value head in the pages: one whose
 queries, keys and values pass a short convolution first and whose window keeps the sequence's first tokens; one
 whose scores are shaped on their way to the softmax (a factor per head, a soft cap, a bias that grows with the
-distance); and the arrangement of two mixers side by side."""
+distance); one that rotates queries and keys and masks by blocks of positions; and the arrangement of two mixers
+side by side."""
 
 from __future__ import annotations
 
@@ -205,6 +206,106 @@ class ShapedWindowAttention(Part):
 
     def forward(self, x, batch, cache):
         return ops.linear(self.readout(ops.linear(x, self.w_in), 0, batch, cache), self.o)
+
+
+@register("mixer", "rotary_chunk_attention")
+class RotaryChunkAttention(Part):
+    """Grouped-query attention with rotated queries and keys over blocks of positions.
+
+    q (``heads`` x ``dim``), k (``kv_heads`` x ``dim``), v (``kv_heads`` x ``vdim``) and, with ``gate``, g (``heads`` x
+    ``vdim``) come from one product with the row-stacked matrix.  With ``bias`` q, k, v and the output projection have
+    biases.  With ``qk_norm`` all of a token's queries together are divided by their root mean square (``eps`` inside
+    the root) and multiplied by a weight of ``heads * dim``, before they are cut into heads; likewise the keys.  Then the
+    first ``position.rotary_dim`` channels of every query and key head turn with the position (``position``: a part of
+    the position family, "rope" pairing channel i with i + dims / 2, "rope_interleaved" 2 i with 2 i + 1; None: no
+    rotation).  Keys and values go to the request's pages, a row [k | v] per token and key/value head.  For query i
+    and key j
+
+        s = (q . k) * scale;    s <- softcap * tanh(s / softcap)   (``softcap`` 0 or None: not),
+
+    and query i sees key j <= i only when ``i // chunk == j // chunk``, the blocks counted from the sequence's start
+    (``chunk`` None: every key up to i).  Softmax in float32; with ``sink`` a learned number per head joins its
+    denominator as ``exp(sink_h)``, once, without a value.  With ``gate`` the heads' results are multiplied element by
+    element by ``sigmoid(g)``.  Then W_o; its bias is handed to whoever adds the result to the stream.
+    A block of positions never reaches further back than ``chunk`` keys, so the pages are a windowed group of that size.
+    params: hidden_size, heads, kv_heads, dim, vdim, scale, chunk, softcap, sink, gate, bias, qk_norm, eps, position."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, H, G, D, Dv = (int(params[k]) for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim"))
+        specs = {"q": WeightSpec((H * D, h)), "k": WeightSpec((G * D, h)), "v": WeightSpec((G * Dv, h)),
+                 "o": WeightSpec((h, H * Dv))}
+        if params.get("bias"):
+            specs.update(q_bias=WeightSpec((H * D,), "bias"), k_bias=WeightSpec((G * D,), "bias"),
+                         v_bias=WeightSpec((G * Dv,), "bias"), o_bias=WeightSpec((h,), "bias"))
+        if params.get("qk_norm"):
+            specs.update(q_norm=WeightSpec((H * D,), "vector"), k_norm=WeightSpec((G * D,), "vector"))
+        if params.get("sink"):
+            specs["sink"] = WeightSpec((H,), "bias")
+        if params.get("gate"):
+            specs["g"] = WeightSpec((H * Dv, h))
+        return specs
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        if dtype == torch.float32:
+            return ("window_attention", "gemm_f32")
+        return ("window_attention", "gemm_bf16", "gemm_bf16_wide")
+
+    hands_over_bias = True
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.heads, self.kv_heads = int(params["heads"]), int(params["kv_heads"])
+        self.dim, self.vdim = int(params["dim"]), int(params["vdim"])
+        if self.kv_heads < 1 or self.heads % self.kv_heads:
+            raise ValueError(f"rotary_chunk_attention: {self.heads} query heads cannot be grouped over "
+                             f"{self.kv_heads} key/value heads")
+        if not (1 <= self.dim <= 256 and 1 <= self.vdim <= 256):
+            raise ValueError(f"rotary_chunk_attention: head sizes {self.dim} x {self.vdim} are refused (1 to 256)")
+        self.scale, self.eps = float(params["scale"]), float(params.get("eps", 1e-6))
+        self.chunk = int(params["chunk"]) if params.get("chunk") else None
+        self.softcap = float(params.get("softcap") or 0.0)
+        mats = [weights["q"], weights["k"], weights["v"]] + ([weights["g"]] if params.get("gate") else [])
+        self.w_in, starts = _stack_rows(mats)
+        self.k_off, self.v_off = starts[1], starts[2]
+        self.g_off = starts[3] if params.get("gate") else None
+        self.q_bias, self.k_bias, self.v_bias = (weights.get(n) for n in ("q_bias", "k_bias", "v_bias"))
+        self.o_bias = weights.get("o_bias")
+        self.q_norm, self.k_norm = weights.get("q_norm"), weights.get("k_norm")
+        self.sinks = weights.get("sink")
+        self.o = weights["o"]
+        pos = params.get("position")
+        self.position, self.rot, self.layout = None, 0, "half"
+        if pos is not None:
+            self.position = ctx.make("position", pos)
+            self.rot = int(self.position.rotary_dim)
+            self.layout = "pairs" if pos.kind == "rope_interleaved" else "half"
+            if self.rot > self.dim:
+                raise ValueError(f"rotary_chunk_attention: {self.rot} turning channels in heads of {self.dim}")
+
+    def cache_spec(self):
+        return PagedKVSpec(self.kv_heads, self.dim + self.vdim, self.chunk, planes=1)
+
+    def activation_widths(self):
+        return [self.w_in.shape[0], self.heads * self.dim, self.heads * self.vdim, self.o.shape[0]]
+
+    def forward(self, x, batch, cache, bias_out=False):
+        p = ops.linear(x, self.w_in)
+        table = batch.block_tables[cache.group]
+        cos, sin = self.position.tables() if self.rot else (None, None)
+        q = ops.qk_rot_append(p, 0, self.k_off, self.v_off, self.q_bias, self.k_bias, self.v_bias, self.q_norm,
+                              self.k_norm, self.eps, cos, sin, self.rot, self.layout, cache.k, table, batch, self.heads,
+                              self.kv_heads, self.dim, self.vdim, write=cache.write)
+        a = ops.window_attention(q, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim, self.scale,
+                                 0, 0, False, softcap=self.softcap, sinks=self.sinks, chunk=self.chunk or 0,
+                                 gate=(p, self.g_off) if self.g_off is not None else None)
+        y = ops.linear(a, self.o)
+        if bias_out:
+            return y, self.o_bias
+        if self.o_bias is not None:
+            y = y + self.o_bias.to(y.dtype)
+        return y
 
 
 def _stack_rows(mats):

@@ -33,7 +33,7 @@ def known_architectures():
 
 
 def _load_builtin() -> None:
-    from .models import llama, nonetar, rezusun, solulix  # noqa: F401  (they register themselves)
+    from .models import llama, nonetar, rezusun, solulix, tevanex  # noqa: F401  (they register themselves)
 
 
 def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
