@@ -458,6 +458,28 @@ def nonetar_config(z, window=1024, streams=4):
             "max_position_embeddings": CONTEXT_LEN}
 
 
+def tevanex_config(z, chunk=1024):
+    """Six layers at the comparison's sizes: a matrix memory (heads of 64 x 64, the state of Solulix's delta rule), an
+    attention with heads of 64 (a quarter as many key/value heads, every channel turning, a sink per head) and one with
+    half as many heads of 128 (half of each head turning with stretched frequencies, capped scores, an output gate), both
+    over blocks of 1024 positions; on every layer 32 experts of a thirty-second of the dense width of which a token uses
+    four, and a shared expert of a quarter."""
+    H = z["heads"]
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 32, "limit": 7.0}, "router": {"experts": 32, "top": 4},
+           "shared": {"ff": z["ff"] // 4, "limit": 7.0}}
+    mem = {"heads": H, "dim": 64, "vdim": 64, "gate_cap": 15.0}
+    att = {"heads": H, "kv_heads": H // 4, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": chunk},
+           "rot": {"base": 10000.0, "dims": 64}}
+    att2 = {"heads": H // 2, "kv_heads": H // 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "mask": {"size": chunk}, "rot": {"base": 10000.0, "dims": 64,
+                                             "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    kinds = [("mlstm", mem), ("attention", att), ("attention_2", att2)]
+    return {"architecture": "Tevanex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "logit_scale": 1.0, "logit_softcap": 30.0,
+            "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": moe} for i in range(z["layers"])],
+            "max_position_embeddings": CONTEXT_LEN}
+
+
 def llama_config_like(z):
     cfg = dict(LLAMA_1B)
     cfg.update(hidden_size=z["width"], intermediate_size=z["ff"], vocab_size=z["vocab"], num_hidden_layers=z["layers"],
@@ -685,6 +707,90 @@ def run_compare_nonetar(size):
             "kernel_roofline_fractions": kernels, "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
 
 
+def run_compare_tevanex(size):
+    """The Tevanex design beside Solulix (the closest design on the engine: attention over [key | value] rows in a
+    windowed page group, a matrix state per head in state slots, routed experts computed for every token) at equal
+    width, depth and vocabulary."""
+    z = COMPARE_SIZES[size]
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    w0 = time.perf_counter()
+    window, keep, chunk = 1024, 64, 1024
+    log(f"{size}: Solulix")
+    sol = measure_design(solulix_config(z, window, keep))
+    log(f"{size}: Tevanex")
+    tev = measure_design(tevanex_config(z, chunk))
+    w1 = time.perf_counter()
+    sampler.stop()
+    T, R, ctx = PREFILL_TOKENS, 64, PROMPT_LEN
+    seen_sol = sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(T))
+    seen = sum(i % chunk + 1 for i in range(T))
+    H, G, W = z["heads"], z["heads"] // 4, z["width"]
+    sol_channels = (H + 2 * G) * 64
+    sol_cols = 32 * (z["ff"] // 16) + z["ff"] // 4
+    cols = 32 * (z["ff"] // 32) + z["ff"] // 4
+    # per token: the product's q, k, v read, the queries written, the rows [k | v] written (the two attentions' mean)
+    qkv_elems = ((H + 2 * G) * 64 + (H // 2 + 2 * (H // 8)) * 128) / 2
+
+    def per_launch(d, phase, key, *names):
+        for name in names:
+            n, ms = d[phase][key].get(name, (0, 0.0))
+            if n:
+                return ms / n
+        return None
+
+    def frac(work, ms, peak_per_s):
+        return None if not ms else round(work / (ms * 1e-3) / peak_per_s, 4)
+    tensor, hbm, fma = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9, FP32_FMA_TFLOPS_NOMINAL * 1e12
+    pre, dec = ("prefill_2048", "operators"), ("decode_b64", "operators_launched")
+    kernels = {
+        "solulix attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen_sol * 4 * H * 64, per_launch(sol, *pre, "flash_attention_rows", "window_attention"), tensor),
+        # both attentions do 2 (dk + dv) heads = 256 H FLOP per seen pair
+        "tevanex window_flash_attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen * 4 * H * 64, per_launch(tev, *pre, "window_flash_attention", "window_attention"), tensor),
+        "solulix window_attention, batch 64 (of the measured copy peak)": frac(
+            R * min(ctx, window + keep) * 2 * G * 64 * 2, per_launch(sol, *dec, "window_attention"), hbm),
+        "tevanex window_attention, batch 64 (of the measured copy peak)": frac(
+            R * min(ctx, chunk) * 2 * G * 64 * 2, per_launch(tev, *dec, "window_attention"), hbm),
+        # both also write the keys and values into their pages
+        "solulix conv_silu, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * sol_channels * 2, per_launch(sol, *pre, "conv_silu"), hbm),
+        "tevanex qk_rot_append, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * qkv_elems * 2, per_launch(tev, *pre, "qk_rot_append"), hbm),
+        "solulix delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * H * 64 * 64 * 10, per_launch(sol, *pre, "delta_scan"), fma),
+        # per element of the memory and token: keep and add (2 FLOP), read out (2); the vector n is 1/64 more
+        "tevanex mlstm_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * H * 64 * 65 * 4, per_launch(tev, *pre, "mlstm_scan"), fma),
+        "solulix delta_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * H * 64 * 64 * 4, per_launch(sol, *dec, "delta_scan"), hbm),
+        "tevanex mlstm_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * H * 64 * 65 * 4, per_launch(tev, *dec, "mlstm_scan"), hbm),
+        "tevanex head_norm_gate, 2048 tokens (of the measured copy peak)": frac(
+            T * H * 64 * 8, per_launch(tev, *pre, "head_norm_gate"), hbm),
+        "solulix join_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 14, per_launch(sol, *pre, "join_norm"), hbm),
+        # the branch output read, the float32 stream read and written, the next sublayer's input written
+        "tevanex add_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 12, per_launch(tev, *pre, "add_norm"), hbm),
+        "solulix expert_act, 2048 tokens (of the measured copy peak)": frac(
+            T * sol_cols * 4, per_launch(sol, *pre, "expert_act"), hbm),
+        # two products read, one activation written
+        "tevanex limited_act, 2048 tokens (of the measured copy peak)": frac(
+            T * cols * 6, per_launch(tev, *pre, "limited_act"), hbm),
+        "solulix route, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * 33 * W * 2, per_launch(sol, *pre, "route"), fma),
+        # the logits come from a matrix product; the kernel reads them and writes the weights
+        "tevanex route, 2048 tokens (of the measured copy peak)": frac(
+            T * (33 + 32) * 4, per_launch(tev, *pre, "route"), hbm),
+    }
+    return {"compare": size, "design": "tevanex", "beside": "solulix", "sizes": z, "window": window, "chunk": chunk,
+            "dtype": "bf16", "data": "synthetic", "peaks": pk, "solulix": sol, "tevanex": tev,
+            "kernel_roofline_fractions": kernels, "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
+
+
 def run_compare(size):
     """The Rezusun design beside Llama at equal width, depth, feed-forward and vocabulary."""
     z = COMPARE_SIZES[size]
@@ -761,12 +867,14 @@ def main():
                     help="instead of the headline: prefill and decode of another design (--design) beside a Llama model of "
                          "equal width, depth, feed-forward and vocabulary (random weights), with the time of every "
                          "operator and roofline fractions of the designs' own kernels; prints its own JSON line")
-    ap.add_argument("--design", default="rezusun", choices=["rezusun", "solulix", "nonetar"],
-                    help="with --compare: which design stands beside Llama (nonetar: beside Solulix, the closest design)")
+    ap.add_argument("--design", default="rezusun", choices=["rezusun", "solulix", "nonetar", "tevanex"],
+                    help="with --compare: which design stands beside Llama (nonetar and tevanex: beside Solulix, the "
+                         "closest design)")
     args = ap.parse_args()
 
     if args.compare:
-        result = {"solulix": run_compare_solulix, "nonetar": run_compare_nonetar}.get(args.design, run_compare)(args.compare)
+        result = {"solulix": run_compare_solulix, "nonetar": run_compare_nonetar,
+                  "tevanex": run_compare_tevanex}.get(args.design, run_compare)(args.compare)
         print(json.dumps(result), flush=True)
         return 0
     if args.impl == "reference":

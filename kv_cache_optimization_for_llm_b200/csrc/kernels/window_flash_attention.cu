@@ -7,7 +7,9 @@
 // swizzled shared memory (two tiles in flight), and runs scores and the weighted sum of values on mma.sync m16n8k16
 // (bfloat16 in, float32 out).  Between the two products every score passes, in float32,
 //     s = (q . k) * scale;  s *= head_scale[h];  s = cap * tanh(s / cap);  s -= slope[h] * (i - j)
-// (each step optional), the mask (j <= i and (i - j < window or j < keep_first)) and the running max/sum softmax.
+// (each step optional), the mask (j <= i and (i - j < window or j < keep_first); or, by blocks of positions counted
+// from the sequence's start, j <= i and i / chunk == j / chunk) and the running max/sum softmax, whose denominator may
+// count a learned score per head once, without a value; the result may be multiplied by the sigmoid of a gate.
 // Key size dk and value size dv are multiples of 8 up to 128; the tiles are padded with zeros to the next of
 // 64 / 128 (keys) and 32 / 64 / 128 (values), which changes no sum.
 #include "common.cuh"
@@ -71,7 +73,7 @@ window_flash_attention_kernel(RowsArgs p) {
   const int pos_first = p.positions[tile.t0];
   const int pos_last = p.positions[tile.t0 + tile.n_tok - 1];
   const int k_hi = pos_last + 1;                                    // keys [.., k_hi) are read
-  const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int k_lo = first_seen_key(pos_first, window, p.shape.chunk);    // positions ascend: no row of the tile sees less
   const int first_tile = k_lo / BN, last_tile = (k_hi - 1) / BN;
   const int keep = window > 0 ? p.keep_first : 0;
   const int keep_tiles = min((keep + BN - 1) / BN, first_tile);
@@ -160,8 +162,8 @@ window_flash_attention_kernel(RowsArgs p) {
         ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3],
                     q_s + swz_pitch<PK>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
       pos_r[0] = row_pos[r0]; pos_r[1] = row_pos[r0 + 8];
-      lo_r[0] = window > 0 ? max(0, pos_r[0] - window + 1) : 0;
-      lo_r[1] = window > 0 ? max(0, pos_r[1] - window + 1) : 0;
+      lo_r[0] = first_seen_key(pos_r[0], window, p.shape.chunk);
+      lo_r[1] = first_seen_key(pos_r[1], window, p.shape.chunk);
     }
     const unsigned char* kt = k_s + buf * BN * PK;
     const unsigned char* vt = v_s + buf * BN * PV;
@@ -256,12 +258,31 @@ window_flash_attention_kernel(RowsArgs p) {
     if (ti >= tile.n_tok || hi >= G) continue;
     if (p.one_more)      // the one more key: score 0, which is 0 in units of log2 too; no value
       l_run[rr] += (m_run[rr] == -CUDART_INF_F) ? 1.f : exp2f(-m_run[rr]);
-    const float inv = l_run[rr] > 0.f ? p.shape.out_scale / l_run[rr] : 0.f;
-    __nv_bfloat16* dst = p.out + ((size_t)(tile.t0 + ti) * p.nq + hk * G + hi) * dv + ((lane & 3) << 1);
+    if (p.shape.sinks != nullptr) {     // the head's learned score, in units of log2 like the running maximum
+      const float sink = p.shape.sinks[hk * G + hi] * kLog2e;
+      if (m_run[rr] == -CUDART_INF_F) {
+        l_run[rr] = 1.f;
+      } else if (sink - m_run[rr] > 100.f) {     // the sink outweighs every key beyond what a float holds: nothing is left
+        l_run[rr] = CUDART_INF_F;
+      } else {
+        l_run[rr] += exp2f(sink - m_run[rr]);
+      }
+    }
+    const float inv = (l_run[rr] > 0.f && l_run[rr] < CUDART_INF_F) ? p.shape.out_scale / l_run[rr] : 0.f;
+    const size_t at = ((size_t)(hk * G + hi)) * dv + ((lane & 3) << 1);
+    __nv_bfloat16* dst = p.out + (size_t)(tile.t0 + ti) * p.nq * dv + at;
+    const __nv_bfloat16* gate = p.shape.gate != nullptr
+        ? static_cast<const __nv_bfloat16*>(p.shape.gate) + (size_t)(tile.t0 + ti) * p.shape.gate_ld + at : nullptr;
 #pragma unroll
     for (int n = 0; n < DT; ++n)
-      if (n * 8 + ((lane & 3) << 1) < dv)
-        *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+      if (n * 8 + ((lane & 3) << 1) < dv) {
+        float a = o[n][rr * 2] * inv, b = o[n][rr * 2 + 1] * inv;
+        if (gate != nullptr) {
+          a *= 1.0f / (1.0f + expf(-__bfloat162float(gate[n * 8])));
+          b *= 1.0f / (1.0f + expf(-__bfloat162float(gate[n * 8 + 1])));
+        }
+        *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(a, b);
+      }
   }
 }
 
@@ -305,15 +326,19 @@ KVB_EXPORT int kvb_window_flash_attention_supported(int dk, int dv, int group, i
 // request, positions ascending, at most (wide ? 128 : 64) / (the group padded to a power of two) of them.
 // q [T, >= nq * dk] with row stride q_row_stride; pages [num_pages, nkv, page_size, dk + dv]; out [T, nq * dv];
 // all bfloat16, q and pages aligned to 16 bytes, q_row_stride a multiple of 8.  head_scale and slopes are
-// float32 [nq] or null; softcap 0 for none; out_scale multiplies the result.
-KVB_EXPORT int kvb_window_flash_attention(const void* q, int q_row_stride, const void* pages, const int* block_table,
-                                          int max_pages, int page_size, int num_pages, const int* positions,
-                                          const void* tiles, int num_tiles, int wide, void* out, int nq, int nkv,
-                                          int dk, int dv, float scale, int window, int keep_first, int one_more,
-                                          const float* head_scale, const float* slopes, float softcap, float out_scale,
-                                          int* status, cudaStream_t stream) {
+// float32 [nq] or null; softcap 0 for none; out_scale multiplies the result.  sinks: float32 [nq] or null; chunk: 0 or
+// the size of the blocks of positions (not together with keep_first); gate: bfloat16 [T, >= nq * dv] with row stride
+// gate_ld, or null.
+KVB_EXPORT int kvb_window_flash_attention_masked(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                                 int max_pages, int page_size, int num_pages, const int* positions,
+                                                 const void* tiles, int num_tiles, int wide, void* out, int nq, int nkv,
+                                                 int dk, int dv, float scale, int window, int keep_first, int one_more,
+                                                 const float* head_scale, const float* slopes, float softcap,
+                                                 float out_scale, const float* sinks, int chunk, const void* gate,
+                                                 int gate_ld, int* status, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nkv < 1 || nkv > 65535 || nq % nkv || window < 0 || keep_first < 0 || softcap < 0.f) return KVB_ERR_BAD_SIZE;
+  if (chunk < 0 || (chunk > 0 && keep_first > 0) || (one_more && sinks != nullptr)) return KVB_ERR_BAD_SIZE;
   const int G = nq / nkv;
   if (!kvb_window_flash_attention_supported(dk, dv, G, page_size)) return KVB_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || (reinterpret_cast<uintptr_t>(pages) & 15))
@@ -328,8 +353,20 @@ KVB_EXPORT int kvb_window_flash_attention(const void* q, int q_row_stride, const
   a.gp_shift = 0;
   while ((1 << a.gp_shift) < G) ++a.gp_shift;
   a.scale = scale; a.window = window; a.keep_first = keep_first; a.one_more = one_more;
-  a.shape = ScoreShape{head_scale, slopes, softcap, out_scale};
+  a.shape = ScoreShape{head_scale, slopes, softcap, out_scale, sinks, chunk, gate, gate_ld};
   a.status = status;
   if (dk <= 64) return wide ? launch_dv<4, 8>(a, num_tiles, stream) : launch_dv<4, 4>(a, num_tiles, stream);
   return wide ? launch_dv<8, 8>(a, num_tiles, stream) : launch_dv<8, 4>(a, num_tiles, stream);
+}
+
+KVB_EXPORT int kvb_window_flash_attention(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                          int max_pages, int page_size, int num_pages, const int* positions,
+                                          const void* tiles, int num_tiles, int wide, void* out, int nq, int nkv,
+                                          int dk, int dv, float scale, int window, int keep_first, int one_more,
+                                          const float* head_scale, const float* slopes, float softcap, float out_scale,
+                                          int* status, cudaStream_t stream) {
+  return kvb_window_flash_attention_masked(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, positions,
+                                           tiles, num_tiles, wide, out, nq, nkv, dk, dv, scale, window, keep_first,
+                                           one_more, head_scale, slopes, softcap, out_scale, nullptr, 0, nullptr, 0,
+                                           status, stream);
 }

@@ -888,15 +888,23 @@ WINDOW_FLASH_WIDE = {"": None, "0": False, "1": True}[os.environ.get('KVB200_WIN
 def window_flash_attention(q: torch.Tensor, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int, dk: int,
                            dv: int, scale: float, window: int, keep_first: int, one_more: bool,
                            head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
-                           softcap: float = 0.0, out_scale: float = 1.0, wide: Optional[bool] = None) -> torch.Tensor:
-    """:func:`window_attention` on tensor cores for bfloat16 steps with runs of query tokens: the same mask, softmax
-    and shaping of the scores (float32), the two products on ``mma.sync`` with the probabilities rounded to bfloat16.
+                           softcap: float = 0.0, out_scale: float = 1.0, wide: Optional[bool] = None,
+                           sinks: Optional[torch.Tensor] = None, chunk: int = 0, gate=None) -> torch.Tensor:
+    """:func:`window_attention` on tensor cores for bfloat16 steps with runs of query tokens: the same mask (window or
+    blocks of ``chunk`` positions), softmax (``sinks`` included), shaping of the scores (float32) and output ``gate``,
+    the two products on ``mma.sync`` with the probabilities rounded to bfloat16.
     Queries at ``q[:, : heads * dk]``; ``pages`` [num_pages, kv_heads, page_size, dk + dv].  Returns [T, heads * dv]."""
     _need_cuda(q, pages)
     assert q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and pages.is_contiguous() and q.stride(1) == 1
     assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
-    for v in (head_scale, slopes):
+    for v in (head_scale, slopes, sinks):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads)
+    gate_at, gate_ld = 0, 0
+    if gate is not None:
+        gt, gcol = gate
+        assert gt.dtype == q.dtype and gt.stride(1) == 1 and gt.shape[0] == q.shape[0] and gt.shape[1] >= gcol + heads * dv
+        assert gcol % 2 == 0 and gt.stride(0) % 2 == 0
+        gate_at, gate_ld = _at(gt, gcol), gt.stride(0)
     T = q.shape[0]
     group = heads // kv_heads
     if wide is None:
@@ -905,12 +913,13 @@ def window_flash_attention(q: torch.Tensor, pages: torch.Tensor, block_table, ba
         wide = (T // rows_tokens_per_tile(group, True)) * kv_heads >= 2 * sm_count(q.device)
     tiles = tiles_of_height(batch, rows_tokens_per_tile(group, bool(wide)))
     out = new((T, heads * dv), q.dtype, q.device)
-    rc = lib("window_flash_attention").kvb_window_flash_attention(
+    rc = lib("window_flash_attention").kvb_window_flash_attention_masked(
         _p(q), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]),
         c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), c_int(1 if wide else 0), _p(out),
         c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_float(scale), c_int(int(window or 0)),
         c_int(int(keep_first or 0)), c_int(1 if one_more else 0), _p(head_scale), _p(slopes), c_float(float(softcap or 0.0)),
-        c_float(float(out_scale)), _p(batch.status), _stream())
+        c_float(float(out_scale)), _p(sinks), c_int(int(chunk or 0)), c_void_p(gate_at), c_int(gate_ld), _p(batch.status),
+        _stream())
     _check(rc, "window_flash_attention")
     choices["window_flash_attention"] += 1
     return out

@@ -42,6 +42,9 @@ def yarn_inv_freq(dims: int, base: float, scaling):
     dims - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair i's frequency is
     ``f_i / factor * ramp_i + f_i (1 - ramp_i)``: fast waves stay, slow ones are divided by ``factor``.  cos and sin
     are multiplied by ``0.1 ln(factor) + 1``.  scaling: factor, original, fast, slow."""
+    for key in ("factor", "original", "fast", "slow"):
+        if scaling.get(key) is None:
+            raise ValueError(f"rope scaling of type 'yarn' needs the key {key!r}")
     i = torch.arange(dims // 2, dtype=torch.float64)
     inv = 1.0 / torch.pow(torch.tensor(float(base), dtype=torch.float64), 2.0 * i / dims)
     factor, original = float(scaling["factor"]), float(scaling["original"])

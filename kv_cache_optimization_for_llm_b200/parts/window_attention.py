@@ -14,7 +14,7 @@ from .. import ops
 from ..cache.specs import PagedKVSpec, PagedWithStateSpec, SlotStateSpec, paged_part, state_part
 from ..weights.loader import WeightSpec
 from .base import Part
-from .registry import register
+from .registry import lookup, register
 
 
 @register("mixer", "conv_window_attention")
@@ -250,7 +250,13 @@ class RotaryChunkAttention(Part):
     def kernel_modules(cls, params, dtype):
         if dtype == torch.float32:
             return ("window_attention", "gemm_f32")
-        return ("window_attention", "gemm_bf16", "gemm_bf16_wide")
+        flash = ("window_flash_attention",) if cls._flash_sizes(params, dtype) else ()
+        return ("window_attention",) + flash + ("gemm_bf16", "gemm_bf16_wide")
+
+    @staticmethod
+    def _flash_sizes(params, dtype, page_size=16):
+        return ops.window_flash_attention_supported(int(params["dim"]), int(params["vdim"]),
+                                                    int(params["heads"]) // max(1, int(params["kv_heads"])), page_size, dtype)
 
     hands_over_bias = True
 
@@ -278,7 +284,8 @@ class RotaryChunkAttention(Part):
         pos = params.get("position")
         self.position, self.rot, self.layout = None, 0, "half"
         if pos is not None:
-            self.position = ctx.make("position", pos)
+            self.position = (ctx.make("position", pos) if ctx.make is not None
+                             else lookup("position", pos.kind)(pos.params, {}, ctx))
             self.rot = int(self.position.rotary_dim)
             self.layout = "pairs" if pos.kind == "rope_interleaved" else "half"
             if self.rot > self.dim:
@@ -290,6 +297,14 @@ class RotaryChunkAttention(Part):
     def activation_widths(self):
         return [self.w_in.shape[0], self.heads * self.dim, self.heads * self.vdim, self.o.shape[0]]
 
+    def query_tile_heights(self):
+        """Tokens per tile of the tensor-core kernel for prompt portions (bfloat16, sizes that are multiples of 8 up to
+        128): the step's batch lays the tiles out for them."""
+        if not self._flash_sizes(self.params, self.ctx.dtype):
+            return []
+        g = self.heads // self.kv_heads
+        return [ops.rows_tokens_per_tile(g, False), ops.rows_tokens_per_tile(g, True)]
+
     def forward(self, x, batch, cache, bias_out=False):
         p = ops.linear(x, self.w_in)
         table = batch.block_tables[cache.group]
@@ -297,9 +312,15 @@ class RotaryChunkAttention(Part):
         q = ops.qk_rot_append(p, 0, self.k_off, self.v_off, self.q_bias, self.k_bias, self.v_bias, self.q_norm,
                               self.k_norm, self.eps, cos, sin, self.rot, self.layout, cache.k, table, batch, self.heads,
                               self.kv_heads, self.dim, self.vdim, write=cache.write)
-        a = ops.window_attention(q, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim, self.scale,
-                                 0, 0, False, softcap=self.softcap, sinks=self.sinks, chunk=self.chunk or 0,
-                                 gate=(p, self.g_off) if self.g_off is not None else None)
+        shape = dict(softcap=self.softcap, sinks=self.sinks, chunk=self.chunk or 0,
+                     gate=(p, self.g_off) if self.g_off is not None else None)
+        if not batch.decode_only and self._flash_sizes(self.params, self.ctx.dtype, cache.page_size):
+            # prompt portions in bfloat16: both products on tensor cores, the scores shaped in float32 between them
+            a = ops.window_flash_attention(q, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                           self.scale, 0, 0, False, **shape)
+        else:
+            a = ops.window_attention(q, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                     self.scale, 0, 0, False, **shape)
         y = ops.linear(a, self.o)
         if bias_out:
             return y, self.o_bias

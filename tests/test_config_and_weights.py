@@ -222,7 +222,9 @@ def test_rotary_part_refuses_a_scaling_it_does_not_know():
     ok = rope_inv_freq(64, 500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                                       "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
     assert ok.shape == (32,)
-    with pytest.raises(ValueError, match="yarn"):
+    with pytest.raises(ValueError, match="longrope"):
+        rope_inv_freq(64, 500000.0, {"rope_type": "longrope", "factor": 8.0})
+    with pytest.raises(ValueError, match="original"):       # a kind it knows, with a key missing
         rope_inv_freq(64, 500000.0, {"rope_type": "yarn", "factor": 8.0})
 
 
