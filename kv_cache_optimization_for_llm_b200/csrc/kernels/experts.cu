@@ -298,12 +298,75 @@ __global__ void limited_act_kernel(const T* __restrict__ p, int ld_p, const floa
   }
 }
 
+// bfloat16 rows whose experts are multiples of 8 features wide: eight results per thread from two 16-byte loads, one
+// look at the token's weight for the expert, and no load at all for an expert that was not chosen.
+__device__ __forceinline__ float limited_one(float g, float u, float w, float limit, float alpha) {
+  g = fminf(w * g, limit);
+  u = fminf(fmaxf(w * u, -limit), limit);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+__global__ void limited_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, int ld_p, const float* __restrict__ gate,
+                                          int ld_gate, const float* __restrict__ shared_logit, int ld_s,
+                                          __nv_bfloat16* __restrict__ out, int E, int F, int S, int width, float limit,
+                                          float shared_limit, float alpha, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const int EF = E * F, gpr = width >> 3;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gpr;
+    const int j = (int)(idx - t * gpr) << 3;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat16* gp = nullptr;
+    const __nv_bfloat16* up = nullptr;
+    float w = 0.f, lim = limit, post = 1.f;
+    if (j < EF) {
+      const int e = j / F, i = j - e * F;
+      w = gate[t * ld_gate + e];
+      gp = p + t * ld_p + 2 * e * F + i;
+      up = gp + F;
+    } else if (j < EF + S) {
+      w = 1.f;
+      lim = shared_limit;
+      gp = p + t * ld_p + 2 * EF + (j - EF);
+      up = gp + S;
+      if (shared_logit != nullptr) post = 1.0f / (1.0f + expf(-shared_logit[t * ld_s]));
+    }
+    if (w != 0.f) {
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gp);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(up);
+      const unsigned gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+      unsigned r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = limited_one(__uint_as_float(gw[k] << 16), __uint_as_float(uw[k] << 16), w, lim, alpha) * post;
+        const float b = limited_one(__uint_as_float(gw[k] & 0xffff0000u), __uint_as_float(uw[k] & 0xffff0000u), w, lim,
+                                    alpha) * post;
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        r[k] = *reinterpret_cast<unsigned*>(&v);
+      }
+      o = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    *reinterpret_cast<uint4*>(out + t * width + j) = o;
+  }
+}
+
 KVB_EXPORT int kvb_limited_act(const void* p, int ld_p, const float* gate, int ld_gate, const float* shared_logit,
                                int ld_s, void* out, int T_, int E, int F, int S, int pad, float limit, float shared_limit,
                                float alpha, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int width = E * F + S + pad;
   if (E < 0 || F < 1 || S < 0 || pad < 0 || E * F + S < 1 || ld_p < 2 * (E * F + S)) return KVB_ERR_BAD_SIZE;
+  if (dtype == KVB_BF16 && F % 8 == 0 && S % 8 == 0 && pad % 8 == 0 && ld_p % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t groups = (size_t)T_ * (width / 8);
+    const size_t want8 = (groups + 255) / 256;
+    const int blocks8 = (int)(want8 < (size_t)kvb_sm_count() * 16 ? want8 : (size_t)kvb_sm_count() * 16);
+    kvb_launch(limited_act_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)p, ld_p, gate, ld_gate,
+               shared_logit, ld_s, (__nv_bfloat16*)out, E, F, S, width, limit, shared_limit, alpha, groups);
+    return kvb_launch_result();
+  }
   const size_t total = (size_t)T_ * width;
   const size_t want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
