@@ -62,13 +62,13 @@ def rotate(x, positions, dims, freqs, grow, layout):
     (i, i + dims / 2) in the layout 'half' and (2i, 2i + 1) in the layout 'pairs'.  The rest passes."""
     out = x.copy()
     half = dims // 2
-    for t, p in enumerate(positions):
-        for i in range(half):
-            a, b = (i, i + half) if layout == "half" else (2 * i, 2 * i + 1)
-            c, s = math.cos(p * freqs[i]) * grow, math.sin(p * freqs[i]) * grow
-            u, v = x[t, :, a].copy(), x[t, :, b].copy()
-            out[t, :, a] = u * c - v * s
-            out[t, :, b] = v * c + u * s
+    pos = np.asarray(list(positions), dtype=np.float64)
+    for i in range(half):
+        a, b = (i, i + half) if layout == "half" else (2 * i, 2 * i + 1)
+        c, s = (np.cos(pos * freqs[i]) * grow)[:, None], (np.sin(pos * freqs[i]) * grow)[:, None]
+        u, v = x[:, :, a], x[:, :, b]
+        out[:, :, a] = u * c - v * s
+        out[:, :, b] = v * c + u * s
     return out
 
 
@@ -76,7 +76,7 @@ def rotate(x, positions, dims, freqs, grow, layout):
 
 def chunk_visible(i, j, size):
     """Query position i sees key position j: not later, and in the same block of ``size`` positions counted from 0."""
-    return j <= i and (size is None or i // size == j // size)
+    return (j <= i) & (True if size is None else (i // size == j // size))       # numbers or arrays
 
 
 def masked_attention(q, k, v, scale, size=None, softcap=None, sinks=None):
@@ -84,18 +84,22 @@ def masked_attention(q, k, v, scale, size=None, softcap=None, sinks=None):
     term exp(sink_h) in the softmax's denominator, which has no value."""
     T, H, _ = q.shape
     G = k.shape[1]
+    seen = chunk_visible(np.arange(T)[:, None], np.arange(T)[None, :], size)
     out = np.zeros((T, H, v.shape[2]))
     for h in range(H):
         g = h // (H // G)
-        for i in range(T):
-            js = [j for j in range(T) if chunk_visible(i, j, size)]
-            s = np.array([q[i, h] @ k[j, g] for j in js]) * scale
-            if softcap:
-                s = soft_cap(s, softcap)
-            top = max(s.max(), sinks[h]) if sinks is not None else s.max()
-            e = np.exp(s - top)
-            denom = e.sum() + (math.exp(sinks[h] - top) if sinks is not None else 0.0)
-            out[i, h] = (e[:, None] * v[js, g]).sum(axis=0) / denom
+        s = (q[:, h] @ k[:, g].T) * scale
+        if softcap:
+            s = soft_cap(s, softcap)
+        s = np.where(seen, s, -np.inf)
+        top = s.max(axis=1)
+        if sinks is not None:
+            top = np.maximum(top, sinks[h])
+        e = np.exp(s - top[:, None])
+        denom = e.sum(axis=1)
+        if sinks is not None:
+            denom = denom + np.exp(sinks[h] - top)
+        out[:, h] = (e @ v[:, g]) / denom[:, None]
     return out
 
 
