@@ -748,8 +748,9 @@ def run_compare_tevanex(size):
         "solulix attention, 2048 tokens (of the measured bf16 peak)": frac(
             seen_sol * 4 * H * 64, per_launch(sol, *pre, "flash_attention_rows", "window_attention"), tensor),
         # both attentions do 2 (dk + dv) heads = 256 H FLOP per seen pair
-        "tevanex window_flash_attention, 2048 tokens (of the measured bf16 peak)": frac(
-            seen * 4 * H * 64, per_launch(tev, *pre, "window_flash_attention", "window_attention"), tensor),
+        # the tcgen05 kernel where its 128-row tiles fill the GPU, else the mma.sync kernel
+        "tevanex attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen * 4 * H * 64, per_launch(tev, *pre, "flash_attention_rows", "window_flash_attention", "window_attention"), tensor),
         "solulix window_attention, batch 64 (of the measured copy peak)": frac(
             R * min(ctx, window + keep) * 2 * G * 64 * 2, per_launch(sol, *dec, "window_attention"), hbm),
         "tevanex window_attention, batch 64 (of the measured copy peak)": frac(

@@ -44,7 +44,16 @@ struct TileDesc { int req, t0, n_tok, pad; };
 //   keep_first     with a window: keys below it are seen whatever the window; the walk over the key
 //                  tiles then starts with the tiles that hold them
 //   one_more       the softmax's denominator counts one more key, of score 0 and without a value
-struct MaskExt { int kv_row_stride, keep_first, one_more; };
+// and, in the tcgen05 kernel with roles only (the others leave them alone; members left out of an initialiser are absent):
+//   chunk          > 0: query i sees key j <= i only when i / chunk == j / chunk, blocks of positions counted from the
+//                  sequence's start (not together with a window)
+//   sinks          float32 [query heads] or null: exp(sinks[h]) joins the denominator once, without a value
+//   softcap        > 0: a scaled score s becomes softcap * tanh(s / softcap)
+//   gate, gate_ld  bfloat16 rows [T, >= nq * d] (row stride gate_ld) by whose sigmoid the result is multiplied
+struct MaskExt {
+  int kv_row_stride, keep_first, one_more;
+  int chunk; const float* sinks; float softcap; const __nv_bfloat16* gate; int gate_ld;
+};
 
 template <int D, int NW, bool EXT>
 __global__ void __launch_bounds__(NW * 32, (D == 64 ? 16 : 8) / NW)
@@ -865,7 +874,8 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
   const int pos_first = positions[tile.t0];
   const int pos_last = positions[tile.t0 + tile.n_tok - 1];
   const int k_hi = pos_last + 1;
-  const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  if (EXT && ext.chunk > 0) k_lo = max(k_lo, pos_first - pos_first % ext.chunk);    // positions ascend: no row sees less
   const int first_tile = k_lo / BNK, last_tile = (k_hi - 1) / BNK;
   // the walk: with EXT first the tiles in front of the window's first that hold kept first keys, then the window's
   const int keep = (EXT && window > 0) ? ext.keep_first : 0;
@@ -982,7 +992,12 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     const int ti = r >> gp_shift, hi = r & (gp - 1);
     const bool row_ok = ti < tile.n_tok && hi < G;
     const int pos = row_ok ? positions[tile.t0 + ti] : -1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (EXT && ext.chunk > 0 && pos >= 0) lo = max(lo, pos - pos % ext.chunk);
+    // a capped score: the raw product x becomes (cap / scale) tanh(x scale / cap), which the scale then turns into
+    // cap tanh(.) like any other score
+    const float cap_in = (EXT && ext.softcap > 0.f) ? scale_log2 * (2.0f / ext.softcap) : 0.f;       // 2 x scale / cap in units of log2
+    const float cap_out = (EXT && ext.softcap > 0.f) ? ext.softcap * 1.4426950408889634f / scale_log2 : 0.f;
     {
       const __nv_bfloat16* src = q_base + (size_t)(tile.t0 + (row_ok ? ti : 0)) * q_row_stride +
                                  (size_t)(hk * G + (row_ok ? hi : 0)) * DH;
@@ -1014,6 +1029,15 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_free[b]);    // this warp has read its rows of S(i)
+      if (EXT && cap_in > 0.f) {
+        // tanh(y) = 1 - 2 / (exp(2 y) + 1): exact at both ends (exp2 gives 0 or infinity there)
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          float rc;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(ex2(v[j] * cap_in) + 1.0f));
+          v[j] = cap_out * fmaf(-2.0f, rc, 1.0f);
+        }
+      }
       if (!plain) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
@@ -1085,12 +1109,33 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       tc_fence_after();
       if (EXT && ext.one_more)       // the one more key: score 0, no value; the sum is in units of 2^m_ref
         l_run += (m_ref == -CUDART_INF_F) ? 1.f : ex2(-m_ref);
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      if (EXT && ext.sinks != nullptr && row_ok) {
+        // the head's learned score, in units of log2 like the running maximum; counted once, no value
+        const float sink = ext.sinks[hk * G + hi] * 1.4426950408889634f;
+        if (m_ref == -CUDART_INF_F) l_run = 1.f;
+        else if (sink - m_ref > 100.f) l_run = CUDART_INF_F;      // it outweighs every key beyond what a float holds
+        else l_run += ex2(sink - m_ref);
+      }
+      const float inv = (l_run > 0.f && l_run < CUDART_INF_F) ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * DH;
+      const __nv_bfloat16* gate = (EXT && ext.gate != nullptr && row_ok)
+          ? ext.gate + (size_t)(tile.t0 + ti) * ext.gate_ld + (size_t)(hk * G + hi) * DH : nullptr;
 #pragma unroll
       for (int half = 0; half < DH / 32; ++half) {
         float o[32];
         tmem_ld32(o_cols + 32 * half, o);
+        if (EXT && gate != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            const uint4 g4 = *reinterpret_cast<const uint4*>(gate + 32 * half + j);
+            const unsigned gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              o[j + 2 * e] *= 1.0f / (1.0f + __expf(-__uint_as_float(gw[e] << 16)));
+              o[j + 2 * e + 1] *= 1.0f / (1.0f + __expf(-__uint_as_float(gw[e] & 0xffff0000u)));
+            }
+          }
+        }
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8)
@@ -1275,4 +1320,35 @@ KVB_EXPORT int kvb_paged_flash_attention_rows(const void* q, int q_row_stride, c
   if (d == 64) { if (wide) KVB_FA_EXT(64, 8); KVB_FA_EXT(64, 4); }
   if (wide) KVB_FA_EXT(128, 8);
   KVB_FA_EXT(128, 4);
+}
+
+// The tcgen05 form with roles (128-row tiles, pages of at least 8 rows) over the same pool [key | value] for mixers
+// that mask by blocks of positions, count a learned score per head into the denominator, cap their scores or gate
+// their result (see MaskExt): query i sees key j <= i when i / chunk == j / chunk (chunk 0: every key up to i).
+// sinks float32 [nq] or null; softcap 0 for none; gate bfloat16 [T, >= nq * d], 16-byte aligned, gate_ld a multiple
+// of 8, or null.
+KVB_EXPORT int kvb_paged_flash_attention_rows_masked(const void* q, int q_row_stride, const void* pages,
+                                                     const int* block_table, int max_pages, int page_size, int num_pages,
+                                                     const int* positions, const void* tiles, int num_tiles, void* out,
+                                                     int nq, int nkv, int d, float scale, int chunk, const float* sinks,
+                                                     float softcap, const void* gate, int gate_ld, int* status,
+                                                     cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (nkv < 1 || nq % nkv || chunk < 0 || softcap < 0.f || !(scale > 0.f)) return KVB_ERR_BAD_SIZE;
+  const int G = nq / nkv;
+  if (!kvb_flash_attention_supported(d, G, page_size) || nkv > 65535 || page_size < 8) return KVB_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || (reinterpret_cast<uintptr_t>(pages) & 15) ||
+      (reinterpret_cast<uintptr_t>(gate) & 15) || (gate != nullptr && (gate_ld & 7)))
+    return KVB_ERR_ALIGN;
+  int gp_shift = 0;
+  while ((1 << gp_shift) < G) ++gp_shift;
+  if ((128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
+  const int page_shift = log2_exact(page_size);
+  const MaskExt ext{2 * d, 0, 0, chunk, sinks, softcap, static_cast<const __nv_bfloat16*>(gate), gate_ld};
+  const void* values = static_cast<const __nv_bfloat16*>(pages) + d;
+  if (d == 64)
+    return tc5::launch_ws<64, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages,
+                                    positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, 0, status, stream, ext);
+  return tc5::launch_ws<128, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages,
+                                   positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, 0, status, stream, ext);
 }

@@ -796,6 +796,53 @@ def flash_attention_rows(q: torch.Tensor, pages: torch.Tensor, block_table, batc
     return out
 
 
+def flash_attention_rows_masked_wanted(batch, heads: int, kv_heads: int, dk: int, dv: int, page_size: int,
+                                       dtype: torch.dtype, q: Optional[torch.Tensor] = None) -> bool:
+    """Whether a step's attention over blocks of positions goes to the tcgen05 kernel with roles: bfloat16, key and value
+    size both 64 or both 128, pages of at least 8 rows, and 128-row tiles enough to fill the GPU (twice over at head
+    size 64), as for the other designs' prompt portions."""
+    if not (dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and page_size >= 8 and FLASH_WIDE and FLASH_TC
+            and FLASH_TC_ROLES and FLASH_ROWS_WIDE in (None, 3)):
+        return False
+    group = heads // kv_heads
+    if not flash_attention_supported(dk, group, page_size):
+        return False
+    if q is not None and not (q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0):
+        return False
+    if FLASH_ROWS_WIDE == 3:
+        return True
+    return (batch.num_tokens // flash_tokens_per_tile(group, True)) * kv_heads >= (2 if dk == 64 else 1) * sm_count(batch.token_ids.device)
+
+
+def flash_attention_rows_masked(q: torch.Tensor, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int,
+                                d: int, scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None,
+                                softcap: float = 0.0, gate=None) -> torch.Tensor:
+    """:func:`window_attention` with a mask by blocks of ``chunk`` positions, ``sinks``, a ``softcap`` and a ``gate`` (as
+    there) on the tcgen05 kernel with roles: bfloat16 steps with runs of query tokens, key and value size ``d`` both
+    (64 or 128), 128-row tiles, pages of at least 8 rows.  Queries at ``q[:, : heads * d]``.  Returns [T, heads * d]."""
+    _need_cuda(q, pages)
+    assert q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and pages.is_contiguous() and q.stride(1) == 1
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], 2 * d)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == heads)
+    T = q.shape[0]
+    gate_at, gate_ld = 0, 0
+    if gate is not None:
+        gt, gcol = gate
+        assert gt.dtype == q.dtype and gt.stride(1) == 1 and gt.shape[0] == T and gt.shape[1] >= gcol + heads * d
+        gate_at, gate_ld = _at(gt, gcol), gt.stride(0)
+    tiles = flash_tiles(batch, heads // kv_heads, True)
+    out = new((T, heads * d), q.dtype, q.device)
+    rc = lib("flash_attention").kvb_paged_flash_attention_rows_masked(
+        _p(q), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]),
+        c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), _p(out), c_int(heads), c_int(kv_heads),
+        c_int(d), c_float(scale), c_int(int(chunk or 0)), _p(sinks), c_float(float(softcap or 0.0)), c_void_p(gate_at),
+        c_int(gate_ld), _p(batch.status), _stream())
+    _check(rc, "flash_attention_rows")
+    choices["flash_attention_rows"] += 1
+    choices["flash_attention_rows_masked"] += 1
+    return out
+
+
 def qk_norm_append(p: torch.Tensor, first: int, k_off: int, v_off: int, bq, bk, bv, qw, kw, eps: float, pages: torch.Tensor,
                    block_table, batch, heads: int, kv_heads: int, dk: int, dv: int, write: bool = True) -> torch.Tensor:
     """What lies between the q|k|v product and an attention over [key | value] rows: the biases (float32, each may

@@ -251,12 +251,19 @@ class RotaryChunkAttention(Part):
         if dtype == torch.float32:
             return ("window_attention", "gemm_f32")
         flash = ("window_flash_attention",) if cls._flash_sizes(params, dtype) else ()
+        if cls._one_size(params, dtype):
+            flash += ("flash_attention",)
         return ("window_attention",) + flash + ("gemm_bf16", "gemm_bf16_wide")
 
     @staticmethod
     def _flash_sizes(params, dtype, page_size=16):
         return ops.window_flash_attention_supported(int(params["dim"]), int(params["vdim"]),
                                                     int(params["heads"]) // max(1, int(params["kv_heads"])), page_size, dtype)
+
+    @staticmethod
+    def _one_size(params, dtype):
+        """Keys and values of one size that the tcgen05 kernel of prompt portions takes (bfloat16, 64 or 128)."""
+        return dtype == torch.bfloat16 and int(params["dim"]) == int(params["vdim"]) and int(params["dim"]) in (64, 128)
 
     hands_over_bias = True
 
@@ -303,7 +310,10 @@ class RotaryChunkAttention(Part):
         if not self._flash_sizes(self.params, self.ctx.dtype):
             return []
         g = self.heads // self.kv_heads
-        return [ops.rows_tokens_per_tile(g, False), ops.rows_tokens_per_tile(g, True)]
+        heights = [ops.rows_tokens_per_tile(g, False), ops.rows_tokens_per_tile(g, True)]
+        if self._one_size(self.params, self.ctx.dtype):
+            heights.append(ops.flash_tokens_per_tile(g, True))
+        return heights
 
     def forward(self, x, batch, cache, bias_out=False):
         p = ops.linear(x, self.w_in)
@@ -314,7 +324,13 @@ class RotaryChunkAttention(Part):
                               self.kv_heads, self.dim, self.vdim, write=cache.write)
         shape = dict(softcap=self.softcap, sinks=self.sinks, chunk=self.chunk or 0,
                      gate=(p, self.g_off) if self.g_off is not None else None)
-        if not batch.decode_only and self._flash_sizes(self.params, self.ctx.dtype, cache.page_size):
+        if (not batch.decode_only and self._one_size(self.params, self.ctx.dtype)
+                and ops.flash_attention_rows_masked_wanted(batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                                           cache.page_size, self.ctx.dtype, q)):
+            # long bfloat16 steps with keys and values of one size, 64 or 128: the tcgen05 kernel with roles
+            a = ops.flash_attention_rows_masked(q, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.scale,
+                                                **shape)
+        elif not batch.decode_only and self._flash_sizes(self.params, self.ctx.dtype, cache.page_size):
             # prompt portions in bfloat16: both products on tensor cores, the scores shaped in float32 between them
             a = ops.window_flash_attention(q, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
                                            self.scale, 0, 0, False, **shape)

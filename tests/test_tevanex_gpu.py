@@ -216,7 +216,7 @@ def _spiked(dtype, chunk, T, query, key, softcap=0.0, sink=None, gate=None, page
     q[query, 3] = 6.0
     k[key] = 0
     k[key, 3] = 5.0
-    Dv = min(T, 128) if flash else T
+    Dv = D if flash == "tcgen05" else (min(T, 128) if flash else T)
     v = np.zeros((T, Dv))
     v[np.arange(T), np.arange(T) % Dv] = 1.0
     g = np.full((T, Dv), 0.0 if gate is None else gate)
@@ -239,7 +239,9 @@ def _spiked(dtype, chunk, T, query, key, softcap=0.0, sink=None, gate=None, page
             ops.kv_rows_append(part, D, 2 * D, pages, batch.block_tables[0], batch, 1, D, Dv)
             shape = dict(softcap=softcap, sinks=None if sink is None else _f32([sink]), chunk=chunk,
                          gate=None if gate is None else (part, 2 * D + Dv))
-            if flash and n > 1:
+            if flash == "tcgen05" and n > 1:
+                got = ops.flash_attention_rows_masked(part, pages, batch.block_tables[0], batch, 1, 1, D, 1.0, **shape)
+            elif flash and n > 1:
                 got = ops.window_flash_attention(part, pages, batch.block_tables[0], batch, 1, 1, D, Dv, 1.0, 0, 0, False, **shape)
             else:
                 got = ops.window_attention(part, 0, pages, batch.block_tables[0], batch, 1, 1, D, Dv, 1.0, 0, 0, False, **shape)
@@ -325,6 +327,62 @@ def test_prompt_portions_on_tensor_cores_see_the_same_keys_and_the_same_sink(wid
     (a, _), ref = _spiked("bfloat16", 16, 64, 63, 50, softcap=4.0, sink=1.0, gate=-1.0, flash=True)
     assert np.abs(a - ref).max() < 2e-2 and ref[50] < 0.27
     assert ops.choices["window_flash_attention"] >= before + 18
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_long_steps_of_one_head_size_on_tcgen05_see_the_same_keys_and_the_same_sink(D):
+    """The tcgen05 kernel with roles, which long bfloat16 steps with keys and values of 64 or of 128 channels use: keys
+    at the edges of the query's block, on tile borders and far away; the sink, the cap and the gate."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    size, T, query = 37, 250, 245            # the query's block starts at 222
+    before = ops.choices["flash_attention_rows_masked"]
+    for key, seen in ((222, True), (221, False), (0, False), (query, True), (223, True), (192, False), (191, False), (185, False)):
+        (in_prompt, _), ref = _spiked("bfloat16", size, T, query, key, flash="tcgen05", D=D)
+        if seen:
+            assert in_prompt[key % D] > 0.99 and abs(in_prompt[key % D] - ref[key % D]) < 1e-2, (key, in_prompt[key % D])
+        assert np.abs(in_prompt - ref).max() < 1e-2, key
+    for key in (2, 0, 63, 64, 127, 128):      # no blocks: every key up to the query, across all tiles
+        (in_prompt, _), ref = _spiked("bfloat16", 0, 250, 249, key, flash="tcgen05", D=D)
+        assert in_prompt[key % D] > 0.99 and np.abs(in_prompt - ref).max() < 1e-2
+    (a, _), ref = _spiked("bfloat16", 0, 64, 63, 19, softcap=4.0, flash="tcgen05", D=D)
+    assert 0.4 < ref[19] < 0.5 and np.abs(a - ref).max() < 2e-2
+    (a, _), ref = _spiked("bfloat16", 0, 64, 63, 19, softcap=4.0, sink=4.0, flash="tcgen05", D=D)
+    assert 0.28 < ref[19] < 0.33 and np.abs(a - ref).max() < 2e-2
+    (a, _), ref = _spiked("bfloat16", 0, 64, 63, 19, softcap=4.0, sink=400.0, flash="tcgen05", D=D)     # beyond what a float holds
+    assert np.abs(a).max() == 0
+    (a, _), ref = _spiked("bfloat16", 16, 64, 63, 50, softcap=4.0, sink=1.0, gate=-1.0, flash="tcgen05", D=D)
+    assert np.abs(a - ref).max() < 2e-2 and ref[50] < 0.27
+    assert ops.choices["flash_attention_rows_masked"] >= before + 18
+
+
+@pytest.mark.parametrize("kind,shape", [
+    ("attention", dict(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, size=50, rot_dims=64)),
+    ("attention_2", dict(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, size=33, rot_dims=32, softcap=30.0, scaling=tiny.YARN)),
+    ("attention_2", dict(heads=2, kv_heads=2, dim=64, vdim=64, scale=0.125, size=None, rot_dims=16, softcap=5.0)),
+])
+def test_the_mixer_on_tcgen05_in_portions_and_beside_another_request(kind, shape, monkeypatch):
+    """The whole mixer with every step that carries a run of tokens on the tcgen05 kernel (as long steps are by
+    themselves), against the plain attention and against the same tokens cut otherwise."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    monkeypatch.setattr(ops, "FLASH_ROWS_WIDE", 3)
+    rng = np.random.default_rng(8)
+    ctx = _ctx("bfloat16")
+    H = 40
+    m = tiny.attention(**shape)
+    wt, w64 = _att_weights(rng, H, m, kind)
+    mixer = _make("mixer", "rotary_chunk_attention", _att_params(H, m, kind), wt, ctx)
+    xs, refs = {}, {}
+    for r, T in enumerate((70, 33)):
+        x, x64 = _w(rng, (T, H), 1.0)
+        xs[r], refs[r] = x.to(torch.bfloat16).cuda(), S.attention_mixer(x64, w64, "", m, kind, 1e-5)
+    before = ops.choices["flash_attention_rows_masked"]
+    whole = _run_in_steps(mixer, ctx, xs, [[(0, 70)], [(1, 33)]])
+    cut = _run_in_steps(mixer, ctx, xs, [[(0, 8), (1, 1)], [(0, 9), (1, 1)], [(0, 2), (1, 30)], [(0, 1), (1, 1)],
+                                         [(0, 44)], [(0, 1)], [(0, 1)], [(0, 4)]])
+    assert ops.choices["flash_attention_rows_masked"] >= before + 7
+    for r in xs:
+        assert _err(whole[r], refs[r], "bfloat16") < TOL["bfloat16"]
+        assert _err(cut[r], refs[r], "bfloat16") < TOL["bfloat16"]
 
 
 # --------------------------------------------------------------------------- the matrix memory
