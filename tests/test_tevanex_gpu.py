@@ -713,14 +713,17 @@ def test_other_orders_of_layers_sizes_and_constants(layers, width, kw, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_greedy_generation_through_the_engine_and_its_scheduler(dtype):
+@pytest.mark.parametrize("which", ["mixed", "attention_only"])
+def test_greedy_generation_through_the_engine_and_its_scheduler(dtype, which):
     """Prompts of unequal length through ``LLM.generate``: the scheduler's portions (a token budget of 24 per step),
     decode steps replayed from CUDA graphs, the engine one step ahead, five requests in three seats.  Every sampled
-    row's logits are compared with the plain model on the final sequences, and in float32 the greedy tokens themselves."""
+    row's logits are compared with the plain model on the final sequences, and in float32 the greedy tokens themselves.
+    The model without a matrix memory has no state of fixed size, so that its lone prompt portions and its steps of
+    single tokens beside one portion are replayed from graphs too (with dummy tokens behind the run)."""
     from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
     from logit_hook import LogitRecorder
     folder = tempfile.mkdtemp(prefix="kvb200_tv_")
-    cfg = tiny.MIXED
+    cfg = tiny.MIXED if which == "mixed" else tiny.ATTENTION_ONLY
     w = tiny.write_model(folder, cfg, seed=4)
     llm = LLM(folder, dtype=dtype, page_size=8, num_pages=48, max_num_seqs=3, max_num_batched_tokens=24,
               max_model_len=128, use_cuda_graphs=True, run_ahead=True)

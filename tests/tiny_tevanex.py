@@ -67,6 +67,14 @@ MIXED = config([layer("mlstm", _M, _F),
                 layer("attention", _A1, moe(experts=3, top=1, ff=16, limit=2.0, shared_ff=0), weights_of=1)])
 
 
+# no mixer with a state of fixed size: the engine may then replay lone prompt portions and mixed steps from graphs
+ATTENTION_ONLY = config([layer("attention", _A1, _F),
+                         layer("attention_2", _A2, moe(experts=4, top=2, ff=8, limit=1.5, shared_ff=8, shared_limit=1.0)),
+                         layer("attention", _A1, _F, weights_of=0),
+                         layer("attention_2", attention(heads=2, kv_heads=1, dim=16, vdim=16, scale=0.25, size=None, rot_dims=16,
+                                                        base=100.0, softcap=6.0), None)], width=32, vocab=61)
+
+
 def expected(cfg):
     from kv_cache_optimization_for_llm_b200.models.spec import expected_weights
     from kv_cache_optimization_for_llm_b200.registry import resolve_architecture
